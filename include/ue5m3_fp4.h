@@ -1,0 +1,154 @@
+/*
+ * C ABI of the B200 (sm_100a) UE5M3/E2M1 quantize + probe-matched GEMM library.
+ *
+ * Every entry point takes borrowed DEVICE pointers (unless a parameter says
+ * "host"), plain sizes and an explicit CUDA stream (a cudaStream_t passed as
+ * void*), launches asynchronously on that stream and returns a status code
+ * (UE5M3_OK == 0).  Nothing here allocates or frees device memory; the caller
+ * owns every buffer.  The library keeps no global state besides a per-process
+ * cache of TMA descriptors encoders (driver entry points).
+ *
+ * Each declaration cites the reference interface it replaces, by the file's
+ * path inside the reference project.
+ */
+#ifndef UE5M3_FP4_H_
+#define UE5M3_FP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UE5M3_ABI_VERSION 1
+
+/* status codes */
+#define UE5M3_OK 0
+#define UE5M3_ERR_INVALID_ARGUMENT 1 /* null pointer, non-positive size, bad enum */
+#define UE5M3_ERR_BLOCK_SIZE 2       /* block size is not 16 or 32 */
+#define UE5M3_ERR_K_NOT_DIVISIBLE 3  /* reduction axis not divisible by block / by 64 */
+#define UE5M3_ERR_ALIGNMENT 4        /* pointer or leading dimension breaks a 16-byte rule */
+#define UE5M3_ERR_UNSUPPORTED 5      /* combination of options not implemented */
+#define UE5M3_ERR_CUDA 6             /* a CUDA runtime / driver call failed */
+#define UE5M3_ERR_SCRATCH 7          /* scratch buffer too small */
+#define UE5M3_ERR_TOO_LARGE 8        /* size exceeds a stated maximum */
+
+/* element types */
+#define UE5M3_DTYPE_BF16 0
+#define UE5M3_DTYPE_FP32 1
+
+/* payload rounding; ids follow the reference, backends/triton/_rounding.py:18-19 */
+#define UE5M3_ROUND_TIES_TO_EVEN 0
+#define UE5M3_ROUND_STOCHASTIC_FAST 7
+
+/* dtype of the explicit random-bit tensor (values 0..255, one per element) */
+#define UE5M3_BITS_NONE 0
+#define UE5M3_BITS_U8 1
+#define UE5M3_BITS_I32 2 /* the reference's dtype, backends/triton/quantization.py:276 */
+
+/* block geometry */
+#define UE5M3_BLOCK_ROW 0 /* 1 x B, along the last axis (activations, dY)          */
+#define UE5M3_BLOCK_COL 1 /* B x 1, along the first axis (wgrad operands)          */
+#define UE5M3_BLOCK_2D 2  /* B x B tiles (weights; formats.py:294-328)             */
+
+/* value domain of the optional fake-quantized tensor output */
+#define UE5M3_FAKE_NONE 0
+#define UE5M3_FAKE_ENCODED 1 /* p*s            backends/triton/quantization.py:135      */
+#define UE5M3_FAKE_DECODED 2 /* (p*s)*dec      backends/triton/quantization.py:136-137  */
+#define UE5M3_FAKE_DEQUANT 3 /* p*(s*dec)      formats.py:439,450                       */
+
+int ue5m3_abi_version(void);
+const char *ue5m3_status_string(int status);
+
+/* Last CUDA error text recorded by this thread's most recent failing call (host string). */
+const char *ue5m3_last_cuda_error(void);
+
+/*
+ * Tensor amax: amax_out[0] = max |x[i]| as fp32, in ONE pass, result left on the
+ * device.  Non-finite inputs make the result +inf or NaN (bit pattern >=
+ * 0x7f800000), which callers test instead of a separate isfinite pass.
+ * Replaces: scaling/training.py:39 (`tensor.to(float32).abs().amax()`),
+ * backends/triton/quantization.py:226.
+ * scratch: ue5m3_amax_scratch_bytes() bytes of device memory, zero-filled once
+ * by the caller before the first use; the kernel leaves it zeroed again.
+ */
+size_t ue5m3_amax_scratch_bytes(void);
+int ue5m3_amax(const void *x, int dtype, int64_t n, float *amax_out, void *scratch,
+               size_t scratch_bytes, void *stream);
+
+/*
+ * Fused single-pass block quantizer: E2M1 payload nibbles + UE5M3 scale bytes
+ * (+ optional fake-quantized tensor) from a [rows, cols] row-major bf16/fp32
+ * tensor and a held tensor amax (device scalar).
+ * Replaces: backends/triton/quantization.py:34-200 (_fake_quantize_operands_kernel)
+ * and formats.py:350-457 (_quantize_dequantize_blocks_impl).
+ *
+ * Packed layouts (byte = element 2j in the low nibble, 2j+1 in the high nibble;
+ * nibble = sign<<3 | index into {0,.5,1,1.5,2,3,4,6}; scale byte = E<<3|M, bias 15):
+ *   BLOCK_ROW: codes   [rows, ceil(cols/2)]   scales   [rows, ceil(cols/B)]
+ *   BLOCK_COL: codes_t [cols, ceil(rows/2)]   scales_t [cols, ceil(rows/B)]
+ *   BLOCK_2D : codes   [rows, ceil(cols/2)]   scales   [ceil(rows/B), ceil(cols/B)]
+ *              codes_t [cols, ceil(rows/2)]   scales_t [ceil(cols/B), ceil(rows/B)]
+ * fake   [rows, cols] and fake_t [cols, rows] hold the values of `fake_domain`
+ * in `fake_dtype`.  Any output pointer may be NULL; outputs a geometry does not
+ * define must be NULL.  Ragged edges are zero padded (formats.py:299-305).
+ * bits: explicit random integers 0..255, same shape as x, required for
+ * UE5M3_ROUND_STOCHASTIC_FAST (backends/triton/quantization.py:270-282).
+ */
+int ue5m3_quantize(const void *x, int dtype, int64_t rows, int64_t cols, int block,
+                   int blocking, const float *amax_dev, float target, int rounding,
+                   const void *bits, int bits_dtype, uint8_t *codes, uint8_t *scales,
+                   uint8_t *codes_t, uint8_t *scales_t, void *fake, void *fake_t,
+                   int fake_dtype, int fake_domain, void *stream);
+
+/*
+ * Packed -> values: out[r,c] = p * (s * dec), formats.py:439,450.
+ * codes [rows, ceil(cols/2)]; scales [rows, ceil(cols/B)] (two_d == 0) or
+ * [ceil(rows/B), ceil(cols/B)] (two_d != 0).
+ */
+int ue5m3_dequantize(const uint8_t *codes, const uint8_t *scales, int64_t rows,
+                     int64_t cols, int block, int two_d, const float *amax_dev,
+                     float target, void *out, int out_dtype, void *stream);
+
+/*
+ * alpha_out[0] = fl(fl(amax_a*amax_b) * inv_denominator): the tensor-scale decode
+ * factor of backends/triton/quantization.py:412-420 with the host scalar
+ * 1/((Ta*6)*(Tb*6)) passed in as fp32.
+ */
+int ue5m3_alpha(const float *amax_a, const float *amax_b, float inv_denominator,
+                float *alpha_out, void *stream);
+
+/*
+ * Probe-matched GEMM on encoded bf16 operands, both K-major:
+ *   out[M,N] = epilogue( A[M,K] * Bt[N,K]^T )
+ * One tcgen05 issue per 64 reduction elements into a fresh TMEM accumulator;
+ * issue partials are combined in ascending k with fp32 round-toward-zero adds;
+ * then, fused: optional RNE snap to the 1/1024 grid, * alpha[0] (device scalar,
+ * NULL = 1), + bias[n] (fp32 or bf16, NULL = none), cast to out_dtype.
+ * Replaces: backends/triton/gemm.py:26-88,110-160 (_issue_rz_kernel,
+ * issue_rz_bf16_gemm), api.py:72-83 and nn/linear.py:334-336.
+ * K % 64 == 0; a, bt 16-byte aligned; ldo = row stride of out in elements.
+ * status_dev (nullable device int[4]): set non-zero if a bounded wait inside the
+ * kernel expired; the kernel then returns without writing the affected tile.
+ */
+int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N, int64_t K,
+                             int snap, const float *alpha_dev, const void *bias,
+                             int bias_dtype, void *out, int out_dtype, int64_t ldo,
+                             int *status_dev, void *stream);
+
+/*
+ * Test hook: compares the software E2M1 ties-to-even rounding with the sm_100a
+ * cvt.rn.satfinite.e2m1x2.f32 instruction over `count` consecutive fp32 bit
+ * patterns starting at `first_bits`; mismatch_count_dev[0] receives the number
+ * of differing finite inputs, first_mismatch_dev[0] the smallest differing
+ * pattern.  No reference counterpart.
+ */
+int ue5m3_test_e2m1_cvt(uint32_t first_bits, uint64_t count,
+                        unsigned long long *mismatch_count_dev,
+                        uint32_t *first_mismatch_dev, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UE5M3_FP4_H_ */
