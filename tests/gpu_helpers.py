@@ -1,0 +1,73 @@
+"""Helpers shared by the GPU parity tests: seeded inputs of the benchmark's value
+distributions and oracle-side restatements of the packed layouts."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import ue5m3_oracle as o
+
+
+def to_np(t: torch.Tensor) -> np.ndarray:
+    return t.detach().float().cpu().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
+
+
+def student_t_dy(rows: int, cols: int, seed: int = 0) -> torch.Tensor:
+    """Upstream-gradient stand-in: Student-t(3) * 1e-3, rounded to bf16."""
+
+    g = torch.Generator().manual_seed(seed)
+    z = torch.randn(rows, cols, generator=g)
+    chi = torch.randn(3, rows, cols, generator=g).square().sum(0)
+    return (z / torch.sqrt(chi / 3.0) * 1e-3).to(torch.bfloat16)
+
+
+def outlier_normal(rows: int, cols: int, seed: int = 0) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    return torch.where(torch.rand(rows, cols, generator=g) < 0.01, x * 100.0, x)
+
+
+def wide_range(rows: int, cols: int, lo: int, seed: int = 0, block: int = 16) -> torch.Tensor:
+    """randn * 2^U{lo..0} per block: adversarial for accumulation order."""
+
+    g = torch.Generator().manual_seed(seed)
+    e = torch.randint(lo, 1, (rows, cols // block), generator=g).float()
+    return torch.randn(rows, cols, generator=g) * torch.exp2(e).repeat_interleave(block, 1)
+
+
+def random_bits(shape, seed: int, dtype=torch.uint8) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 256, tuple(shape), generator=g, dtype=torch.int32).to(dtype)
+
+
+def oracle_quantize(x: torch.Tensor, *, block, blocking, amax, target=448.0, sr=False, bits=None):
+    return o.quantize(
+        to_np(x), block=block, blocking=blocking, amax_value=float(amax), target=target,
+        rounding=o.ROUND_SR if sr else o.ROUND_TTE, rbits=None if bits is None else to_np(bits).astype(np.uint8),
+    )
+
+
+def expect_packed(q: dict) -> dict:
+    """Oracle outputs re-laid as the C ABI lays them out (natural and transposed)."""
+
+    return {
+        "codes": o.pack_nibbles(q["nibbles"]),
+        "codes_t": o.pack_nibbles(np.ascontiguousarray(q["nibbles"].T)),
+        "scales": q["scale_codes"],
+        "scales_t": np.ascontiguousarray(q["scale_codes"].T),
+    }
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).float().numpy()
+
+
+def ulp_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Distance in fp32 units in the last place between two finite fp32 arrays."""
+
+    def key(v):
+        i = np.ascontiguousarray(v, dtype=np.float32).view(np.int32).astype(np.int64)
+        return np.where(i < 0, -(i & 0x7FFFFFFF), i)
+
+    return np.abs(key(a) - key(b))

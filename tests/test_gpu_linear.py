@@ -1,0 +1,153 @@
+"""GPU tests of UE5M3Linear: forward equals the public composition, the three GEMMs take
+the roles / roundings / targets / block geometry of the reference (tests/test_exact_linear.py:
+98-139,298-330), backward matches the oracle with explicit random bits, and the D=50
+lifecycle refreshes at steps 1, 51 and 101 over 120 steps."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_helpers import bf16_round, oracle_quantize, random_bits, to_np
+from oracle import ue5m3_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(in_f, out_f, *, bias, name="layers.0.mixer.up_proj", recipe=None, dtype=torch.bfloat16, seed=0):
+    from ue5m3_fp4.nn import UE5M3Linear
+
+    torch.manual_seed(seed)
+    layer = UE5M3Linear(in_f, out_f, bias=bias, recipe=recipe, backend="probe_matched", module_name=name,
+                        device="cuda", dtype=dtype)
+    with torch.no_grad():
+        layer.weight.copy_(0.02 * torch.randn(out_f, in_f))
+    return layer
+
+
+def test_forward_equals_public_composition():
+    from ue5m3_fp4.backends.triton import probe_matched_fp4_gemm
+
+    layer = _layer(256, 192, bias=True)
+    layer.scale_state.begin_step(1)
+    x = torch.randn(4, 32, 256, device="cuda").to(torch.bfloat16)
+    y = layer(x)
+    flat = x.reshape(-1, 256)
+    ref = probe_matched_fp4_gemm(
+        flat, layer.weight.detach().float().t().contiguous(), block_size=16,
+        tensor_amax_a=flat.float().abs().amax(), tensor_amax_b=layer.weight.detach().float().abs().amax(),
+        two_dimensional_b=True,
+    )
+    ref = (ref + layer.bias.detach().float()).to(torch.bfloat16).reshape(4, 32, 192)
+    assert y.dtype is torch.bfloat16 and torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("name,block", [("layers.45.mixer.down_proj", 16), ("layers.3.mixer.in_proj", 32)])
+def test_backward_matches_oracle_with_explicit_bits(monkeypatch, name, block):
+    import ue5m3_fp4.nn.linear as linear_module
+    from ue5m3_fp4.recipe import UE5M3Recipe
+
+    recipe = UE5M3Recipe.proposed()
+    if block == 32:
+        recipe = UE5M3Recipe.from_dict({**recipe.to_dict(), "block_size": 32, "name": "b32"})
+    tokens, in_f, out_f = 128, 192, 160
+    layer = _layer(in_f, out_f, bias=True, name=name, recipe=recipe, dtype=torch.float32, seed=3)
+    layer.scale_state.begin_step(1)
+    draws = []
+
+    def fixed_bits(reference):
+        bits = random_bits(reference.shape, seed=100 + len(draws), dtype=torch.uint8).to(reference.device)
+        draws.append(bits)
+        return bits
+
+    monkeypatch.setattr(linear_module, "_draw_bits", fixed_bits)
+    g = torch.Generator().manual_seed(9)
+    x = torch.relu(torch.randn(tokens, in_f, generator=g)).square().to(torch.bfloat16).cuda().requires_grad_(True)
+    dy = (1e-4 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16).cuda()
+    y = layer(x)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    assert len(draws) == 2  # separate draws for dgrad and wgrad
+
+    w = layer.weight.detach().float().cpu()
+    xh, dyh = x.detach().float().cpu(), dy.float().cpu()
+    ax, aw, ady = float(xh.abs().max()), float(w.abs().max()), float(dyh.abs().max())
+    t_wdy = recipe.scale_target_for("wgrad_upstream_gradient", name)
+    assert t_wdy == (2048.0 if "down_proj" in name and block == 16 else 448.0) or block == 32
+    qx = oracle_quantize(xh, block=block, blocking=o.BLOCK_ROW, amax=ax)
+    qw = oracle_quantize(w, block=block, blocking=o.BLOCK_2D, amax=aw)
+    yo = o.gemm_issue_rz(qx["encoded"], qw["encoded"], snap=True, alpha_value=o.alpha(np.float32(ax), np.float32(aw), 448.0, 448.0))
+    yo = bf16_round(yo + to_np(layer.bias.detach()))
+    assert np.array_equal(to_np(y), yo)
+    # dgrad: dY rows (stochastic, first draw) x W^T with the same 2-D tiles
+    qdy = oracle_quantize(dyh, block=block, blocking=o.BLOCK_ROW, amax=ady, sr=True, bits=draws[0])
+    dxo = o.gemm_issue_rz(qdy["encoded"], np.ascontiguousarray(qw["encoded"].T), snap=True,
+                          alpha_value=o.alpha(np.float32(ady), np.float32(aw), 448.0, 448.0))
+    assert np.array_equal(to_np(x.grad), bf16_round(dxo))
+    # wgrad: dY^T and X^T, both blocked along the tokens; second draw; T override on dY only
+    qdyt = oracle_quantize(dyh, block=block, blocking=o.BLOCK_COL, amax=ady, target=t_wdy, sr=True, bits=draws[1])
+    qxt = oracle_quantize(xh, block=block, blocking=o.BLOCK_COL, amax=ax)
+    dwo = o.gemm_issue_rz(np.ascontiguousarray(qdyt["encoded"].T), np.ascontiguousarray(qxt["encoded"].T), snap=True,
+                          alpha_value=o.alpha(np.float32(ady), np.float32(ax), t_wdy, 448.0))
+    assert layer.weight.grad.dtype is torch.float32
+    assert np.array_equal(to_np(layer.weight.grad), dwo)
+    assert np.array_equal(to_np(layer.bias.grad), dyh.numpy().sum(0, dtype=np.float32)) or torch.allclose(
+        layer.bias.grad.cpu(), dyh.sum(0), rtol=1e-6, atol=0)
+    keys = {(e["role"], e["module_name"]) for e in layer.scale_state.report()["entries"]}
+    assert keys == {("activation", name), ("weight", name), ("upstream_gradient", name)}
+
+
+def test_delayed_scaling_refreshes_at_1_51_101_over_120_steps():
+    layer = _layer(128, 64, bias=False, name="layers.45.mixer.down_proj")
+    refreshed = []
+    import ue5m3_fp4.scaling.training as training
+
+    original = training.TrainingScaleState._sample_amax
+
+    def counting(tensor):
+        refreshed.append(layer.scale_state.step)
+        return original(tensor)
+
+    layer.scale_state._sample_amax = counting
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for step in range(1, 121):
+        layer.scale_state.begin_step(step)
+        x = (torch.randn(64, 128, device="cuda", generator=g) * (1 + step % 7)).to(torch.bfloat16).requires_grad_(True)
+        layer(x).backward(torch.randn(64, 64, device="cuda", generator=g).to(torch.bfloat16) * 1e-4)
+        layer.weight.grad = None
+    assert sorted(set(refreshed)) == [1, 51, 101]
+    assert len(refreshed) == 9  # activation, weight, upstream gradient at each refresh
+    for entry in layer.scale_state.report()["entries"]:
+        assert (entry["refreshes"], entry["reuses"], entry["last_refresh_step"]) == (3, 117, 101)
+
+
+def test_inference_lifecycle_current_tensor_and_frozen():
+    from ue5m3_fp4.scaling import FP4InferenceScalingController
+
+    model = torch.nn.Sequential()
+    model.add_module("proj", _layer(128, 64, bias=False, name="proj"))
+    model.eval()
+    x = torch.randn(32, 128, device="cuda").to(torch.bfloat16)
+    controller = FP4InferenceScalingController(model, activation_mode="calibrated_frozen",
+                                               checkpoint_identity={"name": "synthetic"})
+    controller.reset_after_checkpoint_load()
+    controller.calibrate_and_freeze_weights()
+    controller.begin_activation_calibration({"set": "unit"})
+    with torch.no_grad():
+        controller.record_activation_calibration_batch(x)
+        model(x)
+        controller.record_activation_calibration_batch(x * 2)
+        model(x * 2)
+    frozen = controller.freeze_activation_scales()
+    assert frozen["proj"]["forward.x"]["amax"] == (x * 2).float().abs().max().item()
+    controller.begin_measurement()
+    with pytest.raises(RuntimeError, match="no_grad"):
+        model(x)
+    with torch.no_grad():
+        y = model(x)
+    assert y.shape == (32, 64)
+    provenance = controller.provenance()
+    assert provenance["numeric_path"] == "quantized_ue5m3_fp4_probe_matched_k64_issue_rz"
+    assert provenance["native_hardware"] is False
+    assert controller.counters()["proj"]["activation_frozen_resolutions"] == 1

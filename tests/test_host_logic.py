@@ -1,0 +1,179 @@
+"""Host-side logic that needs no GPU: recipe, roles and overrides, the D=50 sample-and-hold
+state (with an injected sampler: the real one is a device kernel), distributed amax
+synchronisation (monkeypatched process group and real gloo ranks), conversion, and the
+fail-closed behaviour on CPU tensors.  Mirrors the reference's tests/test_recipe.py,
+tests/test_training_scaling.py, tests/test_conversion.py and tests/test_exact_linear.py:81-95."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from ue5m3_fp4.formats import RoundingMode, normalize_rounding
+from ue5m3_fp4.nn import LinearBackend, UE5M3Linear, convert_linear_modules, exclude_lm_head, select_all_linears
+from ue5m3_fp4.recipe import OperandRole, UE5M3Recipe
+from ue5m3_fp4.scaling import training as training_module
+from ue5m3_fp4.scaling.training import TrainingScaleState, sample_global_amax
+
+
+@pytest.fixture()
+def host_sampler(monkeypatch):
+    """Replace the device reduction by a host stand-in so the lifecycle can be driven on CPU."""
+
+    monkeypatch.setattr(training_module, "_local_amax", lambda t: t.detach().float().abs().amax())
+
+
+def test_rounding_and_role_aliases():
+    assert normalize_rounding("TiesToEven") is RoundingMode.TIES_TO_EVEN
+    assert normalize_rounding("TTE") is RoundingMode.TIES_TO_EVEN
+    assert normalize_rounding("StochasticFast") is RoundingMode.STOCHASTIC_8BIT_MIDPOINT
+    assert normalize_rounding("stochastic-8bit-midpoint") is RoundingMode.STOCHASTIC_8BIT_MIDPOINT
+    with pytest.raises(ValueError, match="unknown rounding mode"):
+        normalize_rounding("ideal_stochastic")
+    recipe = UE5M3Recipe.proposed()
+    assert recipe.normalize_role("dY") is OperandRole.UPSTREAM_GRADIENT
+    assert recipe.normalize_role("x") is OperandRole.ACTIVATION
+    with pytest.raises(ValueError, match="unknown operand role"):
+        recipe.normalize_role("bias")
+
+
+def test_proposed_recipe_roundings_and_targets():
+    recipe = UE5M3Recipe.proposed()
+    assert (recipe.block_size, recipe.delayed_scale_interval, recipe.scale_target) == (16, 50, 448.0)
+    assert recipe.rounding_for("activation") is RoundingMode.TIES_TO_EVEN
+    assert recipe.rounding_for("weight") is RoundingMode.TIES_TO_EVEN
+    assert recipe.rounding_for("upstream_gradient") is RoundingMode.STOCHASTIC_8BIT_MIDPOINT
+    assert recipe.rounding_for("wgrad_dy") is RoundingMode.STOCHASTIC_8BIT_MIDPOINT
+    # The 2048 target applies only to wgrad dY of mixer.down_proj in layers 44..51.
+    assert recipe.scale_target_for("wgrad_upstream_gradient", "layers.45.mixer.down_proj") == 2048.0
+    assert recipe.scale_target_for("upstream_gradient", "layers.45.mixer.down_proj") == 448.0
+    assert recipe.scale_target_for("wgrad_upstream_gradient", "layers.43.mixer.down_proj") == 448.0
+    assert recipe.scale_target_for("wgrad_upstream_gradient", "layers.45.mixer.up_proj") == 448.0
+    assert recipe.scale_target_for("wgrad_upstream_gradient", "model.layers.51.mixer.down_proj") == 2048.0
+
+
+def test_recipe_dict_round_trip_and_strictness(tmp_path):
+    recipe = UE5M3Recipe.proposed()
+    data = recipe.to_dict()
+    assert UE5M3Recipe.from_dict(data) == recipe
+    with pytest.raises(ValueError, match="invalid recipe keys"):
+        UE5M3Recipe.from_dict({**data, "extra": 1})
+    with pytest.raises(ValueError, match="ties-to-even"):
+        UE5M3Recipe.from_dict({**data, "scale_rounding": "StochasticFast"})
+    import yaml
+
+    path = tmp_path / "recipe.yaml"
+    path.write_text(yaml.safe_dump(data))
+    assert UE5M3Recipe.from_yaml(path) == recipe
+    assert UE5M3Recipe.transformer_engine_settings().randomized_hadamard_transform
+
+
+def test_reference_requires_begin_step_and_increasing_steps(host_sampler):
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    with pytest.raises(RuntimeError, match="begin_step"):
+        state.reference("activation", "m", torch.ones(4))
+    with pytest.raises(ValueError, match="positive"):
+        state.begin_step(0)
+    state.begin_step(1)
+    with pytest.raises(ValueError, match="strictly"):
+        state.begin_step(1)
+
+
+def test_d50_is_sample_and_hold_not_a_window_maximum(host_sampler):
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    seen = {}
+    for step in range(1, 52):
+        state.begin_step(step)
+        tensor = {1: torch.tensor([1.0, -3.0]), 51: torch.tensor([1.0, -2.0])}.get(step, torch.tensor([100.0 * step]))
+        seen[step] = state.reference("activation", "layers.0.mixer.in_proj", tensor)
+    assert [seen[s].item() for s in (1, 2, 50, 51)] == [3.0, 3.0, 3.0, 2.0]
+    entry = state.report()["entries"][0]
+    assert (entry["last_refresh_step"], entry["refreshes"], entry["reuses"]) == (51, 2, 49)
+    assert state.state_dict() == {}
+
+
+def test_keys_are_per_role_and_module_and_cadence_starts_at_first_use(host_sampler):
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    state.begin_step(7)
+    assert state.reference("x", "a", torch.tensor([2.0])).item() == 2.0
+    assert state.reference("w", "a", torch.tensor([3.0])).item() == 3.0
+    assert state.reference("x", "b", torch.tensor([4.0])).item() == 4.0
+    assert state.reference("activation", "a", torch.tensor([99.0])).item() == 2.0
+    state.begin_step(56)
+    assert state.reference("x", "a", torch.tensor([56.0])).item() == 2.0
+    state.begin_step(57)
+    assert state.reference("x", "a", torch.tensor([57.0])).item() == 57.0
+    returned = state.reference("x", "a", torch.tensor([1.0]))
+    returned.zero_()  # callers get a clone
+    assert state.reference("x", "a", torch.tensor([1.0])).item() == 57.0
+    assert state.clear_runtime() == 3 and state.step is None
+
+
+def test_sampling_has_no_cpu_path():
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    state.begin_step(1)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        state.reference("activation", "m", torch.ones(4))
+    with pytest.raises(ValueError, match="empty"):
+        sample_global_amax(torch.ones(0), label="x")
+    with pytest.raises(TypeError, match="floating-point"):
+        sample_global_amax(torch.ones(2, dtype=torch.int32), label="x")
+
+
+def test_global_amax_uses_a_max_collective(monkeypatch, host_sampler):
+    calls = []
+
+    def fake_all_reduce(tensor, op=None):
+        calls.append(op)
+        tensor.fill_(11.0)
+
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda: 2)
+    monkeypatch.setattr(dist, "get_backend", lambda: "gloo")
+    monkeypatch.setattr(dist, "all_reduce", fake_all_reduce)
+    assert sample_global_amax(torch.tensor([3.0]), label="t").item() == 11.0
+    assert calls == [dist.ReduceOp.MAX]
+    monkeypatch.setattr(dist, "get_backend", lambda: "nccl")
+    with pytest.raises(RuntimeError, match="NCCL"):
+        sample_global_amax(torch.tensor([3.0]), label="t")
+    monkeypatch.setattr(dist, "get_world_size", lambda: 1)
+    calls.clear()
+    assert sample_global_amax(torch.tensor([3.0]), label="t").item() == 3.0
+    assert calls == []
+
+
+def test_conversion_keeps_parameters_and_rejects_ambiguity():
+    model = torch.nn.Sequential()
+    model.add_module("body", torch.nn.Linear(8, 8, bias=False))
+    model.add_module("lm_head", torch.nn.Linear(8, 4))
+    weight = model.body.weight
+    with pytest.raises(ValueError, match="selector is required"):
+        convert_linear_modules(model)
+    records = convert_linear_modules(model, selector=exclude_lm_head, backend="probe_matched")
+    assert [r.module_name for r in records] == ["body"]
+    assert isinstance(model.body, UE5M3Linear) and model.body.weight is weight
+    assert model.body.backend is LinearBackend.PROBE_MATCHED_TRITON
+    assert model.body.backend.value == "probe_matched_triton_issue_rz"
+    assert isinstance(model.lm_head, torch.nn.Linear) and not isinstance(model.lm_head, UE5M3Linear)
+    shared = torch.nn.Linear(4, 4)
+    tied = torch.nn.ModuleDict({"a": shared, "b": shared})
+    with pytest.raises(ValueError, match="Aliased"):
+        convert_linear_modules(tied, selector=select_all_linears)
+    with pytest.raises(ValueError, match="model root"):
+        convert_linear_modules(torch.nn.Linear(2, 2), selector=select_all_linears)
+
+
+def test_linear_fails_closed_on_cpu_and_reports_contract_strings():
+    layer = UE5M3Linear(64, 32, bias=False, backend="probe_matched", dtype=torch.bfloat16)
+    layer.scale_state.begin_step(1)
+    with pytest.raises(RuntimeError, match="requires CUDA operands"):
+        layer(torch.ones(4, 64, dtype=torch.bfloat16))
+    report = layer.fp4_inference_scaling_report()
+    assert report["format"]["gemm_output_model"] == "encoded_operand_k64_issue_rz_bf16_gemm_final_snap_1_over_1024"
+    assert report["format"]["native_hardware"] is False
+    assert report["format"]["linear_backend"] == "probe_matched_triton_issue_rz"
+    with pytest.raises(ValueError, match="Expected input width"):
+        layer(torch.ones(4, 63, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="unknown UE5M3 linear backend"):
+        UE5M3Linear(4, 4, backend="fastest")

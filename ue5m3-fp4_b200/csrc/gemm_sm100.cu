@@ -248,7 +248,8 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
             mbar_init(&bars->tmem_full[b], 1);
             mbar_init(&bars->tmem_empty[b], kEpilogueWarps);
         }
-        bars->abort_flag = 0;
+        // a launch that follows a recorded failure does no work at all
+        bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(&bars->tmem_base, kTmemCols);
@@ -256,8 +257,11 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *((volatile uint32_t*)&bars->tmem_base);
+    const bool dead = *((volatile int*)&bars->abort_flag) != 0;
 
-    if (warp == 0) {
+    if (dead) {
+        // fall through to the common exit
+    } else if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             for (int j = 0; j < num_issues; ++j) {
