@@ -184,3 +184,265 @@ def run_reference(args) -> None:
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": o.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+class HotPath:
+    """Device-resident state of one rank and the launches of one step."""
+
+    def __init__(self, device, rank: int, world: int) -> None:
+        import torch
+        from ue5m3_fp4.backends import b200
+
+        self.torch, self.ops, self.device, self.world = torch, b200, device, world
+        g = torch.Generator().manual_seed(1000 + rank)  # each data-parallel rank has its own batch
+        gw = torch.Generator().manual_seed(0)  # weights are replicated
+        self.x_host = torch.randn(M, K, generator=g).to(torch.bfloat16).pin_memory()
+        self.x = self.x_host.to(device)
+        self.w = (0.02 * torch.randn(N, K, generator=gw)).to(torch.bfloat16).to(device)
+        self.y_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+        self.amax_w = b200.tensor_amax(self.w).reshape(1)  # held: sampled once at "step 1"
+        self.amax_x = b200.tensor_amax(self.x).reshape(1)
+        self.launches = 0
+        self.gemm_events: list = []
+        self.step_index = 0
+
+    def refresh_activation_amax(self) -> None:
+        """Sample max|X| on the device and MAX all-reduce it across the data-parallel ranks."""
+
+        torch = self.torch
+        self.amax_x = self.ops.tensor_amax(self.x).reshape(1)
+        self.launches += 1
+        if self.world > 1:
+            torch.distributed.all_reduce(self.amax_x, op=torch.distributed.ReduceOp.MAX)
+
+    def step(self, time_gemm: bool = False):
+        torch, ops = self.torch, self.ops
+        if self.step_index % REFRESH_INTERVAL == 0:
+            self.refresh_activation_amax()
+        self.step_index += 1
+        xe = ops.quantize_packed(self.x, block_size=BLOCK, blocking=ops.BLOCK_ROW, tensor_amax=self.amax_x,
+                                 scale_target=TARGET, packed=False, fake_domain="encoded",
+                                 fake_dtype=torch.bfloat16).fake
+        we = ops.quantize_packed(self.w, block_size=BLOCK, blocking=ops.BLOCK_2D, tensor_amax=self.amax_w,
+                                 scale_target=TARGET, packed=False, packed_t=False, fake_domain="encoded",
+                                 fake_dtype=torch.bfloat16).fake
+        alpha = ops.encoded_global_alpha(self.amax_x, self.amax_w, TARGET, TARGET)
+        if time_gemm:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        y = ops.gemm_issue_rz(xe, we, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+        if time_gemm:
+            stop.record()
+            self.gemm_events.append((start, stop))
+        self.launches += 3
+        return y
+
+    def step_e2e(self):
+        """The same step behind host buffers: X from pinned host memory in, Y to pinned host memory out."""
+
+        self.x.copy_(self.x_host, non_blocking=True)
+        y = self.step()
+        self.y_host.copy_(y, non_blocking=True)
+        return y
+
+
+def _timed(torch, dist, world, fn, steps: int) -> float:
+    """Seconds for `steps` calls of fn: barrier + synchronize on both sides, CUDA events, max over ranks."""
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    elapsed = torch.tensor([start.elapsed_time(stop) / 1e3], device="cuda")
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    return float(elapsed.item())
+
+
+def _quantize_headline(torch, ops, device, steps: int, peaks: dict) -> dict:
+    """Backward-operand quantize of dY: bf16 8192x4096, Student-t(3)*1e-3, B=16 1-D blocks,
+    StochasticFast with a seeded uint8 bit tensor, held amax; packed nibbles + scale bytes out."""
+
+    g = torch.Generator().manual_seed(0)
+    z = torch.randn(M, K, generator=g)
+    chi = torch.randn(3, M, K, generator=g).square().sum(0)
+    dy = (z / torch.sqrt(chi / 3.0) * 1e-3).to(torch.bfloat16).to(device)
+    bits = torch.randint(0, 256, (M, K), generator=g, dtype=torch.int32).to(torch.uint8).to(device)
+    amax = ops.tensor_amax(dy).reshape(1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def run(sr: bool) -> float:
+        times = []
+        for i in range(steps + 3):
+            flush.fill_(i & 0xFF)  # evict the 126 MB L2 between launches
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            ops.quantize_packed(dy, block_size=BLOCK, tensor_amax=amax, scale_target=TARGET,
+                                rounding="StochasticFast" if sr else "TTE", random_bits=bits if sr else None)
+            stop.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(start.elapsed_time(stop) * 1e-3)
+        return sum(times) / len(times)
+
+    elems = M * K
+    sr_s, tte_s = run(True), run(False)
+    sr_bytes = elems * (2 + 1 + 0.5 + 1.0 / BLOCK)
+    tte_bytes = elems * (2 + 0.5 + 1.0 / BLOCK)
+    return {
+        "workload": "dY bf16 8192x4096 Student-t(3)*1e-3, B=16, held amax; L2 flushed between launches",
+        "stochastic_u8_bits": {"us": sr_s * 1e6, "achieved_gbs": sr_bytes / sr_s / 1e9,
+                               "frac_of_hbm_peak": sr_bytes / sr_s / 1e9 / peaks["hbm_gbs"],
+                               "algorithmic_bytes": sr_bytes},
+        "ties_to_even": {"us": tte_s * 1e6, "achieved_gbs": tte_bytes / tte_s / 1e9,
+                         "frac_of_hbm_peak": tte_bytes / tte_s / 1e9 / peaks["hbm_gbs"],
+                         "algorithmic_bytes": tte_bytes},
+        "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+    }
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from ue5m3_fp4.backends import b200
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the product arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if not b200.available():
+        raise SystemExit("the sm_100a library is not built: run python ue5m3-fp4_b200/build.py")
+    peaks = _peaks()
+    hot = HotPath(device, rank, world)
+
+    for _ in range(max(args.warmup, 3)):
+        hot.step()
+    hot.launches = 0
+    hot.step_index = 0
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    seconds = _timed(torch, dist, world, lambda: hot.step(time_gemm=True), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = hot.launches
+    b200.check_gemm_status(device)
+    gemm_s = sum(a.elapsed_time(b) for a, b in hot.gemm_events) / len(hot.gemm_events) / 1e3
+
+    for _ in range(2):
+        hot.step_e2e()
+    e2e_seconds = _timed(torch, dist, world, hot.step_e2e, args.steps)
+
+    flops_per_rank = 2.0 * M * N * K
+    value = flops_per_rank * world * args.steps / seconds / 1e12
+    e2e_value = flops_per_rank * world * args.steps / e2e_seconds / 1e12
+    if rank == 0:
+        quant = _quantize_headline(torch, b200, device, max(args.steps, 10), peaks)
+        cpu = cpu_baseline() if world == 1 else None
+        peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        achieved = flops_per_rank / gemm_s / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xue5m3 codes as encoded bf16 -> fp32 RZ accumulate",
+            "data": "synthetic", "config": _config(world),
+            "roofline": {
+                "kernel": "gemm_issue_rz_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
+                "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": None,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (burst {peaks['bf16_tflops']})",
+                "algorithmic_flops_per_launch": flops_per_rank, "gemm_ms": gemm_s * 1e3,
+            },
+            "quantize": quant,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_seconds / args.steps * 1e3,
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "note": "X from pinned host memory in, bf16 Y to pinned host memory out, W resident"},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_case(args) -> None:
+    """Small single-kernel cases for profiler captures (no JSON line, not a benchmark)."""
+
+    import torch
+
+    from ue5m3_fp4.backends import b200
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    if args.case == "gemm-small":
+        m, n = 4096, 8192  # operands + output 160 MB: larger than L2, 2048 tiles
+        a = torch.randn(m, K, generator=g).to(torch.bfloat16).to(device)
+        b = (0.02 * torch.randn(n, K, generator=g)).to(torch.bfloat16).to(device)
+        amax_a, amax_b = b200.tensor_amax(a).reshape(1), b200.tensor_amax(b).reshape(1)
+        ae = b200.quantize_packed(a, block_size=BLOCK, tensor_amax=amax_a, packed=False, fake_domain="encoded",
+                                  fake_dtype=torch.bfloat16).fake
+        be = b200.quantize_packed(b, block_size=BLOCK, blocking=b200.BLOCK_2D, tensor_amax=amax_b, packed=False,
+                                  packed_t=False, fake_domain="encoded", fake_dtype=torch.bfloat16).fake
+        alpha = b200.encoded_global_alpha(amax_a, amax_b, TARGET, TARGET)
+        for _ in range(args.steps):
+            b200.gemm_issue_rz(ae, be, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    else:
+        z = torch.randn(M, K, generator=g)
+        chi = torch.randn(3, M, K, generator=g).square().sum(0)
+        dy = (z / torch.sqrt(chi / 3.0) * 1e-3).to(torch.bfloat16).to(device)
+        bits = torch.randint(0, 256, (M, K), generator=g, dtype=torch.int32).to(torch.uint8).to(device)
+        amax = b200.tensor_amax(dy).reshape(1)
+        w = (0.02 * torch.randn(8192, K, generator=g)).to(torch.bfloat16).to(device)
+        amax_w = b200.tensor_amax(w).reshape(1)
+        for _ in range(args.steps):
+            b200.quantize_packed(dy, block_size=BLOCK, tensor_amax=amax, rounding="StochasticFast", random_bits=bits)
+            b200.quantize_packed(dy, block_size=BLOCK, tensor_amax=amax)
+            b200.quantize_packed(dy, block_size=BLOCK, tensor_amax=amax, packed=False, fake_domain="encoded",
+                                 fake_dtype=torch.bfloat16)
+            b200.quantize_packed(w, block_size=BLOCK, blocking=b200.BLOCK_2D, tensor_amax=amax_w, packed=False,
+                                 packed_t=False, fake_domain="encoded", fake_dtype=torch.bfloat16)
+            b200.quantize_packed(dy, block_size=BLOCK, blocking=b200.BLOCK_COL, tensor_amax=amax,
+                                 rounding="StochasticFast", random_bits=bits, packed=False, packed_t=False,
+                                 fake_domain="encoded", fake_dtype=torch.bfloat16, fake=False, fake_t=True)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(device)
+    print("case", args.case, "done")
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--case", default=None, choices=["gemm-small", "quantize"],
+                        help="run one small kernel case for a profiler capture instead of the benchmark")
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = parser.parse_args()
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
