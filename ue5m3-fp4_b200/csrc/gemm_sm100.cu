@@ -99,12 +99,18 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
 }
 
 // Bounded wait.  Returns false when the budget expired or another role aborted.
+// The clock and the abort flag are looked at once per 32 polls, so the common
+// case is a tight try_wait loop.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity,
                                           GemmBarriers* bars, int* status, int where, int iter) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int spin = 0; spin < 32; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+        for (int spin = 0; spin < 32; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*((volatile int*)&bars->abort_flag)) return false;
         if (clock64() - start > kWaitBudgetClocks) {
             *((volatile int*)&bars->abort_flag) = 1;
@@ -170,8 +176,7 @@ __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
 }
 
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
+__device__ __forceinline__ void tmem_load_32_async(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -183,9 +188,23 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Two fp32 round-toward-zero adds in one instruction (sm_100 packed fp32 pipe).
+__device__ __forceinline__ void fadd2_rz(float& c0, float& c1, uint32_t v0, uint32_t v1) {
+    asm("{\n"
+        ".reg .b64 a, b;\n"
+        "mov.b64 a, {%0, %1};\n"
+        "mov.b64 b, {%2, %3};\n"
+        "add.rz.f32x2 a, a, b;\n"
+        "mov.b64 {%0, %1}, a;\n"
+        "}\n"
+        : "+f"(c0), "+f"(c1)
+        : "r"(v0), "r"(v1));
 }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups
@@ -316,12 +335,18 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!ok) break;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * (kBN / 2));
+            // two 32-column loads in flight per wait; packed round-toward-zero adds
 #pragma unroll
-            for (int chunk = 0; chunk < kBN / 2 / 32; ++chunk) {
-                float v[32];
-                tmem_load_32(taddr + chunk * 32, v);
+            for (int half = 0; half < kBN / 2 / 64; ++half) {
+                uint32_t v0[32], v1[32];
+                tmem_load_32_async(taddr + half * 64, v0);
+                tmem_load_32_async(taddr + half * 64 + 32, v1);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) c[chunk * 32 + i] = __fadd_rz(c[chunk * 32 + i], v[i]);
+                for (int i = 0; i < 32; i += 2) {
+                    fadd2_rz(c[half * 64 + i], c[half * 64 + i + 1], v0[i], v0[i + 1]);
+                    fadd2_rz(c[half * 64 + 32 + i], c[half * 64 + 33 + i], v1[i], v1[i + 1]);
+                }
             }
             tcgen05_fence_before();
             __syncwarp();
