@@ -78,6 +78,24 @@ int ue5m3_amax(const void *x, int dtype, int64_t n, float *amax_out, void *scrat
                size_t scratch_bytes, void *stream);
 
 /*
+ * Tensor amax for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference.  Same result as ue5m3_amax, but the reduction scratch is a fixed array
+ * inside the library (about 4 KiB per GPU that loads the library, held until exit), so
+ * the caller passes only the input, the output and the stream.  Meant for hosts that
+ * have no device allocator of their own to call - a plain C/C++ plugin whose device
+ * memory all belongs to another runtime's pool - and for latency-critical threads where
+ * cudaMalloc's device-wide synchronisation is not acceptable.  The call itself performs
+ * no cudaMalloc/cudaFree and uses no allocating library routine.
+ * Limits and rules:
+ *  - n <= 2^32 elements, otherwise UE5M3_ERR_TOO_LARGE (use ue5m3_amax with own scratch);
+ *  - the first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture;
+ *  - all calls on one device share the one array: calls that may overlap on the GPU
+ *    (different streams, different threads) race and must be serialised by the caller.
+ */
+int ue5m3_amax_static(const void *x, int dtype, int64_t n, float *amax_out, void *stream);
+
+/*
  * Fused single-pass block quantizer: E2M1 payload nibbles + UE5M3 scale bytes
  * (+ optional fake-quantized tensor) from a [rows, cols] row-major bf16/fp32
  * tensor and a held tensor amax (device scalar).

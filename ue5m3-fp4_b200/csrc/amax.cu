@@ -117,6 +117,14 @@ amax_kernel(const void* __restrict__ x, int dtype, int64_t n, float* __restrict_
     finish_amax(thread_amax_bits(x, dtype, n), scratch, out);
 }
 
+// Reduction scratch of ue5m3_amax_static: lives in the library image, one copy per GPU
+// that loads the library, zero at load time.  Host code may not use this name as a
+// pointer; its device address is looked up once per device (static_scratch_for_device).
+static __device__ __align__(256) AmaxScratch g_static_amax_scratch;
+
+constexpr int kMaxDevices = 64;
+constexpr int64_t kStaticAmaxMaxElements = (int64_t)1 << 32;
+
 static int amax_grid(int dtype, int64_t n) {
     int64_t per_thread = dtype == UE5M3_DTYPE_BF16 ? 8 : 4;
     int64_t want = (n + per_thread * kAmaxThreads * 4 - 1) / (per_thread * kAmaxThreads * 4);
@@ -130,7 +138,43 @@ static int amax_grid(int dtype, int64_t n) {
 
 using namespace ue5m3;
 
+// Device address of the static scratch on the current device, resolved on first use.
+static int static_scratch_for_device(AmaxScratch** out) {
+    static AmaxScratch* cache[kMaxDevices] = {nullptr};
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (device < 0 || device >= kMaxDevices) return UE5M3_ERR_UNSUPPORTED;
+    if (cache[device] == nullptr) {
+        void* address = nullptr;
+        e = cudaGetSymbolAddress(&address, g_static_amax_scratch);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        cache[device] = static_cast<AmaxScratch*>(address);
+    }
+    *out = cache[device];
+    return UE5M3_OK;
+}
+
 extern "C" size_t ue5m3_amax_scratch_bytes(void) { return sizeof(AmaxScratch); }
+
+extern "C" int ue5m3_amax_static(const void* x, int dtype, int64_t n, float* amax_out,
+                                 void* stream_v) {
+    if (!x || !amax_out || n <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (n > kStaticAmaxMaxElements) {
+        record_error_text("ue5m3_amax_static: more than 2^32 elements; use ue5m3_amax with caller scratch");
+        return UE5M3_ERR_TOO_LARGE;
+    }
+    AmaxScratch* scratch = nullptr;
+    int status = static_scratch_for_device(&scratch);
+    if (status != UE5M3_OK) return status;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    // The ticket must start at zero; the array keeps whatever the previous call left.
+    cudaError_t e = cudaMemsetAsync(&scratch->ticket, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    amax_kernel<<<amax_grid(dtype, n), kAmaxThreads, 0, stream>>>(x, dtype, n, amax_out, scratch);
+    return check_launch();
+}
 
 extern "C" int ue5m3_amax(const void* x, int dtype, int64_t n, float* amax_out, void* scratch,
                           size_t scratch_bytes, void* stream_v) {
