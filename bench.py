@@ -271,36 +271,56 @@ def _timed(torch, dist, world, fn, steps: int) -> float:
 
 def _quantize_headline(torch, ops, device, steps: int, peaks: dict) -> dict:
     """Backward-operand quantize of dY: bf16 8192x4096, Student-t(3)*1e-3, B=16 1-D blocks,
-    StochasticFast with a seeded uint8 bit tensor, held amax; packed nibbles + scale bytes out."""
+    StochasticFast with a seeded uint8 bit tensor, held amax; packed nibbles + scale bytes out.
 
-    g = torch.Generator().manual_seed(0)
-    z = torch.randn(M, K, generator=g)
-    chi = torch.randn(3, M, K, generator=g).square().sum(0)
-    dy = (z / torch.sqrt(chi / 3.0) * 1e-3).to(torch.bfloat16).to(device)
-    bits = torch.randint(0, 256, (M, K), generator=g, dtype=torch.int32).to(torch.uint8).to(device)
-    amax = ops.tensor_amax(dy).reshape(1)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    Kernel-only timing through the C ABI with preallocated outputs: `steps` back-to-back
+    launches between two CUDA events, rotating over four distinct input sets (4 x 100 MB,
+    larger than the 126 MB L2) so that every launch reads from HBM."""
+
+    from ue5m3_fp4 import _native
+
+    lib = _native.load()
+    sets = []
+    for seed in range(4):
+        g = torch.Generator().manual_seed(seed)
+        z = torch.randn(M, K, generator=g)
+        chi = torch.randn(3, M, K, generator=g).square().sum(0)
+        dy = (z / torch.sqrt(chi / 3.0) * 1e-3).to(torch.bfloat16).to(device)
+        bits = torch.randint(0, 256, (M, K), generator=g, dtype=torch.int32).to(torch.uint8).to(device)
+        sets.append((dy, bits))
+    amax = ops.tensor_amax(sets[0][0]).reshape(1)
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=device)
+    scales = torch.empty((M, K // BLOCK), dtype=torch.uint8, device=device)
+    stream = _native.stream_ptr(device)
+
+    def launch(i: int, sr: bool) -> None:
+        dy, bits = sets[i % 4]
+        status = lib.ue5m3_quantize(
+            dy.data_ptr(), _native.DTYPE_BF16, M, K, BLOCK, _native.BLOCK_ROW, amax.data_ptr(), TARGET,
+            _native.ROUND_STOCHASTIC_FAST if sr else _native.ROUND_TIES_TO_EVEN,
+            bits.data_ptr() if sr else None, _native.BITS_U8 if sr else _native.BITS_NONE,
+            codes.data_ptr(), scales.data_ptr(), None, None, None, None, 0, 0, stream)
+        _native.check(status, "ue5m3_quantize")
 
     def run(sr: bool) -> float:
-        times = []
-        for i in range(steps + 3):
-            flush.fill_(i & 0xFF)  # evict the 126 MB L2 between launches
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            ops.quantize_packed(dy, block_size=BLOCK, tensor_amax=amax, scale_target=TARGET,
-                                rounding="StochasticFast" if sr else "TTE", random_bits=bits if sr else None)
-            stop.record()
-            torch.cuda.synchronize()
-            if i >= 3:
-                times.append(start.elapsed_time(stop) * 1e-3)
-        return sum(times) / len(times)
+        for i in range(4):
+            launch(i, sr)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            launch(i, sr)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e-3 / steps
 
     elems = M * K
     sr_s, tte_s = run(True), run(False)
     sr_bytes = elems * (2 + 1 + 0.5 + 1.0 / BLOCK)
     tte_bytes = elems * (2 + 0.5 + 1.0 / BLOCK)
     return {
-        "workload": "dY bf16 8192x4096 Student-t(3)*1e-3, B=16, held amax; L2 flushed between launches",
+        "workload": "dY bf16 8192x4096 Student-t(3)*1e-3, B=16, held amax; four rotating input sets (> L2)",
+        "launches_timed": steps,
         "stochastic_u8_bits": {"us": sr_s * 1e6, "achieved_gbs": sr_bytes / sr_s / 1e9,
                                "frac_of_hbm_peak": sr_bytes / sr_s / 1e9 / peaks["hbm_gbs"],
                                "algorithmic_bytes": sr_bytes},
@@ -352,7 +372,7 @@ def run_ours(args) -> None:
     value = flops_per_rank * world * args.steps / seconds / 1e12
     e2e_value = flops_per_rank * world * args.steps / e2e_seconds / 1e12
     if rank == 0:
-        quant = _quantize_headline(torch, b200, device, max(args.steps, 10), peaks)
+        quant = _quantize_headline(torch, b200, device, max(args.steps, 40), peaks)
         cpu = cpu_baseline() if world == 1 else None
         peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         achieved = flops_per_rank / gemm_s / 1e12

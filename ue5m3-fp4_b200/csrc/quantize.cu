@@ -2,9 +2,9 @@
 //
 // Two kernels:
 //  * quantize_row_kernel   1 x B blocks along the contiguous axis.  Pure
-//    streaming: one 128-bit load per 8 elements, block amax by warp shuffle
-//    between the B/8 lanes of a block, one 32-bit packed-nibble store per lane,
-//    one scale byte per block.  HBM bound.
+//    streaming: one 256-bit load per 16 elements (one thread owns a B=16 block;
+//    two lanes share a B=32 block through one shuffle), one 64-bit packed-nibble
+//    store per thread, one scale byte per block.  HBM bound.
 //  * quantize_tile_kernel  B x 1 blocks along the strided axis and B x B tiles.
 //    A 128 x 64 tile is staged in shared memory so that the strided-axis blocks
 //    are read without bank conflicts and every global access stays coalesced;
@@ -100,68 +100,153 @@ __device__ __forceinline__ void store_fake8(void* fake, int fake_dtype, int64_t 
 }
 
 // ---------------------------------------------------------------------------
-// 1 x B blocks along the contiguous axis; the tensor is viewed as a flat run of
-// 8-element chunks (cols % B == 0, so chunks and blocks never straddle rows).
+// 1 x B blocks along the contiguous axis.  The tensor is viewed as a flat run of
+// 16-element units (cols % B == 0, so units and blocks never straddle rows); one
+// thread owns one unit per step: a 256-bit load of the values, a 128-bit load of
+// the random bytes, one 64-bit store of 16 nibbles and one scale byte.  With
+// B = 16 a thread owns the whole block (no shuffle); with B = 32 two lanes share.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7])
+                 : "l"(p));
+}
+
+// (a, b) * (s, s) with one packed fp32 instruction, round-to-nearest
+__device__ __forceinline__ void mul2_rn(float& a, float& b, float s) {
+    asm("{\n"
+        ".reg .b64 x, y;\n"
+        "mov.b64 x, {%0, %1};\n"
+        "mov.b64 y, {%2, %2};\n"
+        "mul.rn.f32x2 x, x, y;\n"
+        "mov.b64 {%0, %1}, x;\n"
+        "}\n"
+        : "+f"(a), "+f"(b)
+        : "f"(s));
+}
+
+template <typename T>
+__device__ __forceinline__ void load_unit(const T* x, int64_t unit, float (&v)[16]);
+
+template <>
+__device__ __forceinline__ void load_unit<__nv_bfloat16>(const __nv_bfloat16* x, int64_t unit, float (&v)[16]) {
+    uint32_t w[8];
+    ldg256(x + unit * 16, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+template <>
+__device__ __forceinline__ void load_unit<float>(const float* x, int64_t unit, float (&v)[16]) {
+    uint32_t w[8];
+    ldg256(x + unit * 16, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(w[i]);
+    ldg256(x + unit * 16 + 8, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[8 + i] = __uint_as_float(w[i]);
+}
+
+// 16 random bytes of one unit, packed four per word
+template <int BITS>
+__device__ __forceinline__ void load_unit_bits(const void* bits, int64_t unit, uint32_t (&r)[4]) {
+    if (BITS == UE5M3_BITS_U8) {
+        uint4 w = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(bits) + unit * 16));
+        r[0] = w.x; r[1] = w.y; r[2] = w.z; r[3] = w.w;
+    } else {
+        const int32_t* p = static_cast<const int32_t*>(bits) + unit * 16;
+        uint32_t w[8];
+        ldg256(p, w);
+        r[0] = (w[0] & 0xFFu) | ((w[1] & 0xFFu) << 8) | ((w[2] & 0xFFu) << 16) | (w[3] << 24);
+        r[1] = (w[4] & 0xFFu) | ((w[5] & 0xFFu) << 8) | ((w[6] & 0xFFu) << 16) | (w[7] << 24);
+        ldg256(p + 8, w);
+        r[2] = (w[0] & 0xFFu) | ((w[1] & 0xFFu) << 8) | ((w[2] & 0xFFu) << 16) | (w[3] << 24);
+        r[3] = (w[4] & 0xFFu) | ((w[5] & 0xFFu) << 8) | ((w[6] & 0xFFu) << 16) | (w[7] << 24);
+    }
+}
+
+// r14 = (2r + 1) << 14 of byte k of a packed word
+__device__ __forceinline__ uint32_t r14_of(uint32_t word, int k) {
+    uint32_t shifted = k == 0 ? (word << 15) : k == 1 ? (word << 7) : k == 2 ? (word >> 1) : (word >> 9);
+    return (shifted & 0x7F8000u) | 0x4000u;
+}
+
 template <typename T, int B, int RMODE, int BITS>
 __global__ void __launch_bounds__(256)
-quantize_row_kernel(const T* __restrict__ x, int64_t nchunks, const float* __restrict__ amax_dev,
-                    float six_t, const void* __restrict__ bits, uint32_t* __restrict__ codes,
+quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __restrict__ amax_dev,
+                    float six_t, const void* __restrict__ bits, uint2* __restrict__ codes,
                     uint8_t* __restrict__ scales, void* __restrict__ fake, int fake_dtype,
                     int fake_domain) {
-    constexpr int kLanesPerBlock = B / 8;
-    constexpr int kUnroll = 4;
+    constexpr int kLanesPerBlock = B / 16;
+    constexpr int kUnroll = 2;
     const TensorScale ts = tensor_scale(__ldg(amax_dev), six_t);
     const int64_t stride = (int64_t)gridDim.x * (256 * kUnroll);
-    for (int64_t base = (int64_t)blockIdx.x * (256 * kUnroll); base < nchunks; base += stride) {
-        float v[kUnroll][8];
-        uint32_t r14[kUnroll][8];
+    for (int64_t base = (int64_t)blockIdx.x * (256 * kUnroll); base < nunits; base += stride) {
+        float v[kUnroll][16];
+        uint32_t rb[kUnroll][4];
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k) {
-            int64_t chunk = base + k * 256 + threadIdx.x;
-            if (chunk < nchunks) {
-                load8<T>(x + chunk * 8, v[k]);
-                if (RMODE == kRoundSr) load_bits8<BITS>(bits, chunk * 8, r14[k]);
+            int64_t unit = base + k * 256 + threadIdx.x;
+            if (unit < nunits) {
+                load_unit<T>(x, unit, v[k]);
+                if (RMODE == kRoundSr) load_unit_bits<BITS>(bits, unit, rb[k]);
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { v[k][i] = 0.0f; r14[k][i] = 0u; }
+                for (int i = 0; i < 16; ++i) v[k][i] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rb[k][i] = 0u;
             }
         }
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k) {
-            int64_t chunk = base + k * 256 + threadIdx.x;
+            int64_t unit = base + k * 256 + threadIdx.x;
             float m = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[k][i]));
+            for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[k][i]));
+            if (kLanesPerBlock == 2) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+            const uint32_t code = block_scale_code(m, ts);
+            const float scale = ue5m3_decode(code);
+            const float rcp = payload_multiplier(scale, ts);
 #pragma unroll
-            for (int o = 1; o < kLanesPerBlock; o <<= 1)
-                m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-            uint32_t code = block_scale_code(m, ts);
-            float scale = ue5m3_decode(code);
-            float rcp = payload_multiplier(scale, ts);
-            float u[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) u[i] = __fmul_rn(v[k][i], rcp);
-            uint32_t packed;
+            for (int i = 0; i < 16; i += 2) mul2_rn(v[k][i], v[k][i + 1], rcp);
+            uint32_t packed[2];
             if (RMODE == kRoundTteHw) {
-                packed = e2m1_pack8_hw(u);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float u[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) u[i] = v[k][h * 8 + i];
+                    packed[h] = e2m1_pack8_hw(u);
+                }
             } else {
-                packed = 0u;
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    packed |= e2m1_nibble<RMODE == kRoundSr>(u[i], r14[k][i]) << (4 * i);
+                for (int h = 0; h < 2; ++h) {
+                    packed[h] = 0u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        uint32_t r14 = RMODE == kRoundSr ? r14_of(rb[k][(h * 8 + i) / 4], i & 3) : 0u;
+                        packed[h] |= e2m1_nibble<RMODE == kRoundSr>(v[k][h * 8 + i], r14) << (4 * i);
+                    }
+                }
             }
-            if (chunk < nchunks) {
-                if (codes) codes[chunk] = packed;
-                if (scales && (threadIdx.x % kLanesPerBlock) == 0)
-                    scales[chunk / kLanesPerBlock] = (uint8_t)code;
+            if (unit < nunits) {
+                if (codes) codes[unit] = make_uint2(packed[0], packed[1]);
+                if (scales && (kLanesPerBlock == 1 || (threadIdx.x & 1) == 0))
+                    scales[unit / kLanesPerBlock] = (uint8_t)code;
                 if (fake) {
-                    float f[8];
-                    float sd = __fmul_rn(scale, ts.dec);
+                    const float sd = __fmul_rn(scale, ts.dec);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        f[i] = fake_value((packed >> (4 * i)) & 0xFu, scale, sd, ts.dec, fake_domain);
-                    store_fake8(fake, fake_dtype, chunk * 8, f);
+                    for (int h = 0; h < 2; ++h) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            f[i] = fake_value((packed[h] >> (4 * i)) & 0xFu, scale, sd, ts.dec, fake_domain);
+                        store_fake8(fake, fake_dtype, unit * 16 + h * 8, f);
+                    }
                 }
             }
         }
@@ -531,14 +616,14 @@ static bool use_hw_cvt() {
 }
 
 template <typename T, int B, int RMODE, int BITS>
-static void launch_row(const void* x, int64_t nchunks, const float* amax_dev, float six_t,
+static void launch_row(const void* x, int64_t nunits, const float* amax_dev, float six_t,
                        const void* bits, uint8_t* codes, uint8_t* scales, void* fake,
                        int fake_dtype, int fake_domain, cudaStream_t stream) {
-    int64_t want = (nchunks + 1023) / 1024;
+    int64_t want = (nunits + 511) / 512;
     int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
     quantize_row_kernel<T, B, RMODE, BITS><<<grid, 256, 0, stream>>>(
-        static_cast<const T*>(x), nchunks, amax_dev, six_t, bits,
-        reinterpret_cast<uint32_t*>(codes), scales, fake, fake_dtype, fake_domain);
+        static_cast<const T*>(x), nunits, amax_dev, six_t, bits,
+        reinterpret_cast<uint2*>(codes), scales, fake, fake_dtype, fake_domain);
 }
 
 template <typename T, int B>
@@ -619,10 +704,12 @@ extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t co
 
     if (blocking == UE5M3_BLOCK_ROW) {
         const bool fake_vec = !fake || (((uintptr_t)fake % 16) == 0 && (cols * fsize) % 16 == 0);
-        const bool fast = cols % block == 0 && x_vec && bits_vec && fake_vec &&
-                          (!codes || ((uintptr_t)codes % 4) == 0);
+        const bool bits32 = !sr || (bits_dtype == UE5M3_BITS_U8 ? ((uintptr_t)bits % 16) == 0
+                                                                : ((uintptr_t)bits % 32) == 0);
+        const bool fast = cols % block == 0 && x_vec && bits_vec && fake_vec && bits32 &&
+                          ((uintptr_t)x % 32) == 0 && (!codes || ((uintptr_t)codes % 8) == 0);
         if (fast) {
-            int64_t nchunks = rows * cols / 8;
+            int64_t nchunks = rows * cols / 16;
 #define UE5M3_DR(T, B) \
     dispatch_row<T, B>(rmode, bits_dtype, x, nchunks, amax_dev, six_t, bits, codes, scales, fake, fake_dtype, fake_domain, stream)
             if (dtype == UE5M3_DTYPE_BF16) { if (block == 16) UE5M3_DR(__nv_bfloat16, 16); else UE5M3_DR(__nv_bfloat16, 32); }

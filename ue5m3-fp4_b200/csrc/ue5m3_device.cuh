@@ -63,7 +63,7 @@ __device__ __forceinline__ uint32_t block_scale_code(float block_amax, const Ten
 
 // Reciprocal-then-multiply payload multiplier (formats.py:439-443).
 __device__ __forceinline__ float payload_multiplier(float scale, const TensorScale& t) {
-    return __fdiv_rn(1.0f, __fmul_rn(scale, t.dec));
+    return __frcp_rn(__fmul_rn(scale, t.dec));  // correctly rounded, same bits as 1/d
 }
 
 // ---- E2M1 rounding -------------------------------------------------------
