@@ -24,7 +24,8 @@ namespace ue5m3 {
 
 enum : int { kRoundTteHw = 0, kRoundTteSw = 1, kRoundSr = 2 };
 
-__device__ __forceinline__ uint32_t r14_from_byte(uint32_t r) { return (r << 15) | 0x4000u; }
+// (2r + 1) << 14 plus the 4 << 23 bias that e2m1_index_sr expects
+__device__ __forceinline__ uint32_t r14_from_byte(uint32_t r) { return (r << 15) | 0x02004000u; }
 
 // Load 8 consecutive elements as fp32.
 template <typename T>
@@ -172,7 +173,7 @@ __device__ __forceinline__ void load_unit_bits(const void* bits, int64_t unit, u
 // r14 = (2r + 1) << 14 of byte k of a packed word
 __device__ __forceinline__ uint32_t r14_of(uint32_t word, int k) {
     uint32_t shifted = k == 0 ? (word << 15) : k == 1 ? (word << 7) : k == 2 ? (word >> 1) : (word >> 9);
-    return (shifted & 0x7F8000u) | 0x4000u;
+    return (shifted & 0x7F8000u) | 0x02004000u;
 }
 
 template <typename T, int B, int RMODE, int BITS>
@@ -229,7 +230,7 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         uint32_t r14 = RMODE == kRoundSr ? r14_of(rb[k][(h * 8 + i) / 4], i & 3) : 0u;
-                        packed[h] |= e2m1_nibble<RMODE == kRoundSr>(v[k][h * 8 + i], r14) << (4 * i);
+                        packed[h] += e2m1_nibble<RMODE == kRoundSr>(v[k][h * 8 + i], r14) * (1u << (4 * i));
                     }
                 }
             }
@@ -238,13 +239,18 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
                 if (scales && (kLanesPerBlock == 1 || (threadIdx.x & 1) == 0))
                     scales[unit / kLanesPerBlock] = (uint8_t)code;
                 if (fake) {
+                    // hardware nibble decode, then the multiplier chain of the requested domain
                     const float sd = __fmul_rn(scale, ts.dec);
+                    const float first = fake_domain == UE5M3_FAKE_DEQUANT ? sd : scale;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         float f[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            f[i] = fake_value((packed[h] >> (4 * i)) & 0xFu, scale, sd, ts.dec, fake_domain);
+                        for (int i = 0; i < 8; i += 2) {
+                            e2m1_unpack2_hw((packed[h] >> (4 * i)) & 0xFFu, f[i], f[i + 1]);
+                            mul2_rn(f[i], f[i + 1], first);
+                            if (fake_domain == UE5M3_FAKE_DECODED) mul2_rn(f[i], f[i + 1], ts.dec);
+                        }
                         store_fake8(fake, fake_dtype, unit * 16 + h * 8, f);
                     }
                 }

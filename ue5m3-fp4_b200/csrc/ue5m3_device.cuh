@@ -7,6 +7,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -79,18 +80,21 @@ __device__ __forceinline__ uint32_t e2m1_index_tte(float a) {
 }
 
 // 8-bit-midpoint stochastic rounding (formats.py:196-200): away from zero iff
-// fl(delta + (2r+1)*2^-9) >= 1.  r14 = (2r+1) << 14.
+// fl(delta + (2r+1)*2^-9) >= 1.  r14 = ((2r+1) << 14) | (4 << 23).
 //  * a >= 1: delta = low22/2^22 and the sum is exact, so the rule is the carry
-//    of 2*bits + r14 into bit 23.
+//    of 2*bits + (2r+1)<<14 into bit 23; (2*bits + r14) >> 23 is then
+//    0xFC + 4 + index, i.e. the index modulo 8 (the 4 << 23 in r14 supplies the 4).
 //  * a <  1: quantum 0.5, significand 2a; z = fl(2a + mid) is the reference's
 //    own fp32 add when a < 0.5 (lower = 0) and is exact for a in [0.5, 1);
-//    floor(z) is the index.
+//    floor(z) is the index, read from the low bits of RZ(z + 2^23).
+// Returns a word whose low three bits are the magnitude index.
 __device__ __forceinline__ uint32_t e2m1_index_sr(float a, uint32_t r14) {
     uint32_t b = __float_as_uint(a);
-    uint32_t hi = ((b * 2u + r14) >> 23) - 0xFCu;
+    uint32_t hi = (b * 2u + r14) >> 23;
+    // bit 25 of r14 is already set in 0x3F800000, so the OR sees only (2r+1) << 14
     float mid = __fadd_rn(__uint_as_float(0x3F800000u | r14), -1.0f);  // (2r+1)*2^-9, exact
     float z = __fmaf_rn(a, 2.0f, mid);
-    uint32_t lo = __float_as_uint(__fadd_rz(z, 8388608.0f)) & 3u;
+    uint32_t lo = __float_as_uint(__fadd_rz(z, 8388608.0f));
     return b >= 0x3F800000u ? hi : lo;
 }
 
@@ -103,7 +107,8 @@ template <bool kStochastic>
 __device__ __forceinline__ uint32_t e2m1_nibble(float u, uint32_t r14) {
     float a = fminf(fabsf(u), 6.0f);
     uint32_t idx = kStochastic ? e2m1_index_sr(a, r14) : e2m1_index_tte(a);
-    return idx | ((__float_as_uint(u) >> 28) & 8u);
+    // low three bits from idx, bit 3 from the sign of u (u >> 28 has the sign in bit 3)
+    return (idx & 7u) | ((__float_as_uint(u) >> 28) & ~7u);
 }
 
 __device__ __forceinline__ float e2m1_value(uint32_t nibble) {
@@ -128,6 +133,22 @@ __device__ __forceinline__ uint32_t e2m1_pack8_hw(const float (&u)[8]) {
         : "=r"(out)
         : "f"(u[0]), "f"(u[1]), "f"(u[2]), "f"(u[3]), "f"(u[4]), "f"(u[5]), "f"(u[6]), "f"(u[7]));
     return out;
+}
+
+// Hardware decode of one packed byte (two nibbles) to two floats: lo = low nibble.
+__device__ __forceinline__ void e2m1_unpack2_hw(uint32_t byte, float& lo, float& hi) {
+    uint32_t h2;
+    asm("{\n"
+        ".reg .b8 b;\n"
+        "cvt.u8.u32 b, %1;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b;\n"
+        "}\n"
+        : "=r"(h2)
+        : "r"(byte));
+    __half2 h = *reinterpret_cast<__half2*>(&h2);
+    float2 f = __half22float2(h);
+    lo = f.x;
+    hi = f.y;
 }
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
