@@ -143,6 +143,7 @@ def _cpu_step(x, w) -> float:
 def cpu_baseline(budget_s: float = 12.0) -> dict:
     from oracle import ue5m3_oracle as o
 
+    o.set_threads(os.cpu_count() or 1)  # launchers may have exported OMP_NUM_THREADS=1
     rows, cols = 64, 256
     x, w = _cpu_sample_inputs(rows, cols)
     probe = _cpu_step(x, w)
@@ -168,6 +169,7 @@ def run_reference(args) -> None:
         return
     from oracle import ue5m3_oracle as o
 
+    o.set_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1
     rows, cols = 256, 1024
     x, w = _cpu_sample_inputs(rows, cols)
     for _ in range(args.warmup):
@@ -351,13 +353,13 @@ def run_ours(args) -> None:
     peaks = _peaks()
     hot = HotPath(device, rank, world)
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # samples cover warm-up (same work) and the timed region
     for _ in range(max(args.warmup, 3)):
         hot.step()
     hot.launches = 0
     hot.step_index = 0
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     seconds = _timed(torch, dist, world, lambda: hot.step(time_gemm=True), args.steps)
     clocks = sampler.stop() if rank == 0 else None
     launches = hot.launches
@@ -452,7 +454,7 @@ def main() -> None:
     parser.add_argument("--case", default=None, choices=["gemm-small", "quantize"],
                         help="run one small kernel case for a profiler capture instead of the benchmark")
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = parser.parse_args()

@@ -68,6 +68,8 @@ def lib() -> ctypes.CDLL:
         handle.ue5m3o_alpha.restype = f32
         handle.ue5m3o_alpha.argtypes = [f32, f32, f32, f32, ctypes.c_int]
         handle.ue5m3o_num_threads.restype = ctypes.c_int
+        handle.ue5m3o_set_threads.restype = None
+        handle.ue5m3o_set_threads.argtypes = [ctypes.c_int]
         _lib = handle
     return _lib
 
@@ -253,6 +255,10 @@ def probe_matched_fp4_gemm(
     )
     al = alpha(amax_a, amax_b, target_a, target_b, reciprocal_alpha)
     return gemm_issue_rz(qa["encoded"], qb["encoded"], snap=snap, alpha_value=al)
+
+
+def set_threads(n: int) -> None:
+    lib().ue5m3o_set_threads(int(n))
 
 
 def num_threads() -> int:
