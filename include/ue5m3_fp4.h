@@ -156,6 +156,34 @@ int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N
                              int *status_dev, void *stream);
 
 /*
+ * UE5M3 scale bytes -> the block-scaled tensor core's UE4M3 scale-factor layout.
+ * scales: [rows, K/block] (two_d == 0) or [ceil(rows/block), K/block] (two_d != 0) as written
+ * by ue5m3_quantize for a K-major operand.  sf_out: ue5m3_packed_scales_bytes(rows, K) bytes,
+ * [ceil(rows/128)][K/64][512]; within a 512-byte atom the byte of row r0 + 32*r1 and 16-block
+ * kb sits at r0*16 + r1*4 + kb.  Each byte is the UE5M3 byte minus ((8 + shift) << 3), i.e.
+ * the same scale divided by 2^shift in UE4M3; window_flag[0] (device int) is set to 1 when a
+ * scale does not fit UE4M3's normal range at that shift.  No reference counterpart (the
+ * reference has no packed operands).
+ */
+size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K);
+int ue5m3_pack_scales_ue4m3(const uint8_t *scales, int64_t rows, int64_t K, int block, int two_d,
+                            int shift, uint8_t *sf_out, int *window_flag, void *stream);
+
+/*
+ * Probe-matched GEMM on PACKED operands with the FP4 block-scaled tensor cores:
+ *   out[M,N] = epilogue( 2^shift_sum * sum over K=64 issues of (A codes x scales) . (B codes x scales) )
+ * a_codes [M, K/2], b_codes [N, K/2] (E2M1 nibbles, reduction axis contiguous); a_sf, b_sf from
+ * ue5m3_pack_scales_ue4m3; shift_sum = shift_a + shift_b.  One MMA instruction per K=64 issue,
+ * accumulated by the tensor core in FP32; epilogue as ue5m3_gemm_issue_rz_bf16 (snap, alpha,
+ * bias, cast).  Replaces the same reference code as ue5m3_gemm_issue_rz_bf16
+ * (backends/triton/gemm.py:26-160, api.py:72-83).  K % 64 == 0, (K/2) % 16 == 0.
+ */
+int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
+                   const uint8_t *b_sf, int64_t M, int64_t N, int64_t K, int shift_sum, int snap,
+                   const float *alpha_dev, const void *bias, int bias_dtype, void *out,
+                   int out_dtype, int64_t ldo, int *status_dev, void *stream);
+
+/*
  * Test hook: compares the software E2M1 ties-to-even rounding with the sm_100a
  * cvt.rn.satfinite.e2m1x2.f32 instruction over `count` consecutive fp32 bit
  * patterns starting at `first_bits`; mismatch_count_dev[0] receives the number

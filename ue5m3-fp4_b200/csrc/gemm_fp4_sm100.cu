@@ -1,0 +1,472 @@
+// Packed-FP4 GEMM on the sm_100a block-scaled tensor cores.
+//
+//   out[M,N] = epilogue( sum_k  A[m,k] * B[n,k] ),   A, B = E2M1 codes x per-16 block scales
+//
+// Operands are the packed outputs of the quantizer (two E2M1 nibbles per byte, reduction
+// axis contiguous).  The block scales are UE5M3 bytes re-biased to the tensor core's UE4M3
+// scale type by a per-tensor power of two (ue5m3_pack_scales_ue4m3 below): both formats
+// carry three fraction bits, so inside a 15-binade window the re-biased scale is the same
+// number divided by 2^shift, and the epilogue multiplies the result by 2^(shift_a+shift_b),
+// which is exact.  A scale outside the window raises the caller's window flag; the caller
+// then uses the BF16-issue kernel (gemm_sm100.cu), which has no such restriction.
+//
+// One tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X instruction multiplies a
+// 128 x 256 x 64 slab, i.e. exactly one K=64 issue of the reference model (four 16-blocks
+// per operand row), and accumulates it into the FP32 tile in TMEM; the K loop is a plain
+// chain of such instructions.
+//
+// Tiling: persistent CTAs (one per SM) walk 128 x 256 output tiles.  A stage holds K = 256
+// (128 bytes per row, one 128-byte swizzle atom): A 16 KiB + B 32 KiB + scale atoms 2 + 4 KiB;
+// four stages.  Warp 0 = TMA/bulk-copy producer, warp 1 = scale copies (shared -> TMEM) and
+// MMA issue, warps 2..9 = epilogue (lane quadrant = warp % 4, column half = (warp - 2) / 4).
+// All waits are clock-bounded.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "abi_common.cuh"
+#include "tcgen05_ptx.cuh"
+
+namespace ue5m3 {
+
+using namespace ptx;
+
+constexpr int kFM = 128;            // tile rows
+constexpr int kFN = 256;            // tile columns
+constexpr int kFKStage = 256;       // reduction elements per stage (128 bytes per row)
+constexpr int kFKMma = 64;          // reduction elements per MMA = one issue
+constexpr int kFStages = 4;
+constexpr int kFThreads = 320;
+constexpr int kFEpilogueWarps = 8;
+constexpr uint32_t kFTmemCols = 512;
+constexpr uint32_t kSfAtomBytes = 512;  // 128 rows x 4 scale bytes
+constexpr uint32_t kFBytesA = kFM * kFKStage / 2;
+constexpr uint32_t kFBytesB = kFN * kFKStage / 2;
+constexpr uint32_t kFBytesSfa = 4 * kSfAtomBytes;
+constexpr uint32_t kFBytesSfb = 8 * kSfAtomBytes;
+constexpr uint32_t kFStageBytes = kFBytesA + kFBytesB + kFBytesSfa + kFBytesSfb;
+// TMEM columns: accumulator 0..255, scale slots of A from 256 (4 per MMA), of B from 320 (8 per MMA)
+constexpr uint32_t kTmemSfa = 256;
+constexpr uint32_t kTmemSfb = 320;
+
+struct Fp4Params {
+    int M, N, K;
+    int snap;
+    float rescale;  // 2^(shift_a + shift_b)
+    const float* alpha;
+    const void* bias;
+    int bias_dtype;
+    void* out;
+    int out_dtype;
+    long long ldo;
+    int* status;
+    const uint8_t* sfa;  // [ceil(M/128)][K/64][512]
+    const uint8_t* sfb;  // [ceil(N/128)][K/64][512]
+    int tiles_m, tiles_n;
+};
+
+struct __align__(8) Fp4Barriers {
+    unsigned long long full[kFStages];
+    unsigned long long empty[kFStages];
+    unsigned long long tmem_full;
+    unsigned long long tmem_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// D[tmem] (+)= A[smem] * B[smem] with per-16 block scales read from TMEM.
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                         uint32_t idesc, uint32_t accumulate, uint32_t tmem_sfa,
+                                         uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// 32 rows x 16 bytes from shared memory into 4 TMEM columns of every lane quadrant.
+__device__ __forceinline__ void tmem_copy_sf(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+                 : "memory");
+}
+
+// Instruction descriptor of the block-scaled kind: A = B = E2M1 (code 1), both K-major,
+// UE4M3 scales, K = 64.
+__host__ __device__ constexpr uint32_t make_idesc_fp4(int m, int n) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// tile index -> (tile_m, tile_n): groups of 8 tile rows sweep the tile columns together
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tile_m, int& tile_n) {
+    constexpr int kGroupM = 8;
+    const int tiles_per_group = kGroupM * tiles_n;
+    const int group = tile / tiles_per_group;
+    const int first_m = group * kGroupM;
+    const int group_m = (tiles_m - first_m) < kGroupM ? (tiles_m - first_m) : kGroupM;
+    tile_m = first_m + (tile % tiles_per_group) % group_m;
+    tile_n = (tile % tiles_per_group) / group_m;
+}
+
+// Persistent: CTA c works on tiles c, c + gridDim.x, ...  The accumulator is drained into
+// registers by eight epilogue warps right after a tile's last MMA and released at once, so
+// the next tile's MMAs overlap the epilogue arithmetic and the global stores.
+__global__ void __launch_bounds__(kFThreads, 1)
+gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const Fp4Params p) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    Fp4Barriers* bars = reinterpret_cast<Fp4Barriers*>(smem + kFStages * kFStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_issues = p.K / kFKMma;          // MMAs along K
+    const int num_stages = (num_issues + 3) / 4;  // stages along K
+    const int sf_k = num_issues;                  // scale atoms per row tile
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kFStages; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+        }
+        mbar_init(&bars->tmem_full, 1);
+        mbar_init(&bars->tmem_empty, kFEpilogueWarps);
+        bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&bars->tmem_base, kFTmemCols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *((volatile uint32_t*)&bars->tmem_base);
+    const bool dead = *((volatile int*)&bars->abort_flag) != 0;
+
+    if (dead) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        // ---------------- producer: operands by TMA, scale atoms by bulk copy ----------------
+        if (lane == 0) {
+            uint32_t g = 0;  // stage counter across tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int tile_m, tile_n;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+                const int m0 = tile_m * kFM, n0 = tile_n * kFN;
+                const bool second_b_tile = (2 * tile_n + 1) * 128 < p.N;  // columns 128..255 exist
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kFStages;
+                    const uint32_t use = g / kFStages;
+                    if (use > 0) {
+                        ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 1, j);
+                        if (!ok) break;
+                    }
+                    unsigned char* sa = smem + s * kFStageBytes;
+                    unsigned char* sb = sa + kFBytesA;
+                    unsigned char* ssfa = sb + kFBytesB;
+                    unsigned char* ssfb = ssfa + kFBytesSfa;
+                    const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
+                    const uint32_t sf_bytes = (uint32_t)issues_here * kSfAtomBytes;
+                    const uint32_t tx = kFBytesA + kFBytesB + sf_bytes * (second_b_tile ? 3u : 2u);
+                    mbar_arrive_expect_tx(&bars->full[s], tx);
+                    tma_load_2d(sa, &map_a, &bars->full[s], j * (kFKStage / 2), m0);
+                    tma_load_2d(sb, &map_b, &bars->full[s], j * (kFKStage / 2), n0);
+                    bulk_load(ssfa, p.sfa + ((size_t)tile_m * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                              &bars->full[s]);
+                    bulk_load(ssfb, p.sfb + ((size_t)(2 * tile_n) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                              &bars->full[s]);
+                    if (second_b_tile)
+                        bulk_load(ssfb + 4 * kSfAtomBytes,
+                                  p.sfb + ((size_t)(2 * tile_n + 1) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                                  &bars->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- scale copies + MMA issue ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_fp4(kFM, kFN);
+            uint32_t g = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                if (it > 0) {  // the previous tile must have left the accumulator
+                    ok = mbar_wait(&bars->tmem_empty, (it - 1) & 1, &bars->abort_flag, p.status, 2, it);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                }
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kFStages;
+                    ok = mbar_wait(&bars->full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * kFStageBytes);
+                    const uint32_t sb = sa + kFBytesA;
+                    const uint32_t ssfa = sb + kFBytesB;
+                    const uint32_t ssfb = ssfa + kFBytesSfa;
+                    const uint64_t desc_a = smem_desc_sw128(sa);
+                    const uint64_t desc_b = smem_desc_sw128(sb);
+                    const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
+                    for (int k = 0; k < issues_here; ++k) {
+                        const uint32_t slot = (uint32_t)(s * 4 + k);
+                        const uint32_t t_sfa = tmem_base + kTmemSfa + slot * 4;
+                        const uint32_t t_sfb = tmem_base + kTmemSfb + slot * 8;
+                        tmem_copy_sf(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
+                        tmem_copy_sf(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
+                        tmem_copy_sf(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                        // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                        umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                 (j > 0 || k > 0) ? 1u : 0u, t_sfa, t_sfb);
+                    }
+                    umma_commit(&bars->empty[s]);
+                }
+                if (ok) umma_commit(&bars->tmem_full);
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers (release) -> arithmetic -> global ----------------
+        const int q = warp & 3;          // TMEM lane quadrant
+        const int h = (warp - 2) >> 2;   // column half of the tile
+        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            int tile_m, tile_n;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+            bool ok = mbar_wait(&bars->tmem_full, it & 1, &bars->abort_flag, p.status, 4, it);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
+            uint32_t v[4][32];
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) tmem_load_32_async(taddr + chunk * 32, v[chunk]);
+            tmem_wait_ld();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty);
+
+            const long long row = (long long)tile_m * kFM + q * 32 + lane;
+            if (row >= p.M) continue;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
+                if (col0 >= p.N) continue;
+                float c[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __fmul_rn(__uint_as_float(v[chunk][i]), p.rescale);
+                    if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
+                    if (p.alpha) x = __fmul_rn(x, alpha);
+                    c[i] = x;
+                }
+                if (p.bias) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        int col = col0 + i;
+                        if (col < p.N) {
+                            float bv = p.bias_dtype == UE5M3_DTYPE_BF16
+                                           ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
+                                           : static_cast<const float*>(p.bias)[col];
+                            c[i] = __fadd_rn(c[i], bv);
+                        }
+                    }
+                }
+                if (p.out_dtype == UE5M3_DTYPE_BF16) {
+                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+                    const bool vec = (p.ldo % 8) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (vec && col0 + i + 8 <= p.N) {
+                            uint4 w;
+                            uint32_t hb[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                hb[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + e]));
+                            w.x = hb[0] | (hb[1] << 16); w.y = hb[2] | (hb[3] << 16);
+                            w.z = hb[4] | (hb[5] << 16); w.w = hb[6] | (hb[7] << 16);
+                            *reinterpret_cast<uint4*>(out + i) = w;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (col0 + i + e < p.N) out[i + e] = __float2bfloat16_rn(c[i + e]);
+                        }
+                    }
+                } else {
+                    float* out = static_cast<float*>(p.out) + row * p.ldo + col0;
+                    const bool vec = (p.ldo % 4) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (vec && col0 + i + 4 <= p.N) {
+                            *reinterpret_cast<float4*>(out + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col0 + i + e < p.N) out[i + e] = c[i + e];
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kFTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// UE5M3 scale bytes -> UE4M3 scale bytes in the tensor core's scale-factor layout.
+//
+// Output: [ceil(rows/128)][K/64][512 bytes]; inside a 512-byte atom the byte of row
+// r = r0 + 32*r1 (r0 < 32, r1 < 4) and 16-block kb (< 4) sits at r0*16 + r1*4 + kb.
+// Source scales are [rows/row_group][K/block] bytes (row_group = 1 for 1-D blocks, = block
+// for 2-D tiles); a 32-wide block feeds two consecutive 16-blocks.
+// byte_out = byte_in - ((8 + shift) << 3): same fraction bits, exponent re-biased from 15 to
+// 7 and divided by 2^shift.  Valid UE4M3 exponents are 1..15 (and not 0x7F); anything else
+// raises *window_flag.  Rows beyond `rows` get 1.0 (0x38).
+// ---------------------------------------------------------------------------------------
+__global__ void pack_scales_kernel(const uint8_t* __restrict__ scales, int64_t rows, int64_t kblocks,
+                                   int block, int row_group, int shift, uint32_t* __restrict__ out,
+                                   int64_t row_tiles, int64_t k_atoms, int* __restrict__ window_flag) {
+    const int64_t total = row_tiles * k_atoms * 128;
+    const int per16 = block / 16;
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int word = (int)(i % 128);           // r0 * 4 + r1
+        const int64_t atom = i / 128;              // tile * k_atoms + ka
+        const int64_t ka = atom % k_atoms, tile = atom / k_atoms;
+        const int r0 = word >> 2, r1 = word & 3;
+        const int64_t row = tile * 128 + r1 * 32 + r0;
+        uint32_t packed = 0x38383838u;
+        if (row < rows) {
+            packed = 0u;
+            const uint8_t* src = scales + (row / row_group) * kblocks;
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                const int64_t h = ka * 4 + kb;     // 16-wide block index along K
+                int code5 = src[h / per16];
+                int code4 = code5 - ((8 + shift) << 3);
+                if (code4 < 8 || code4 > 0x7E) {
+                    bad = true;
+                    code4 = code4 < 8 ? 8 : 0x7E;
+                }
+                packed |= (uint32_t)code4 << (8 * kb);
+            }
+        }
+        out[atom * 128 + word] = packed;
+    }
+    if (bad) atomicExch(window_flag, 1);
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 fp4_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
+            query != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+// [rows, K/2] bytes row-major -> 2-D map with a (128 byte x box_rows) box, 128B swizzle.
+static int make_codes_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k_bytes,
+                          uint32_t box_rows) {
+    PFN_cuTensorMapEncodeTiled_v12000 encode = fp4_encode_fn();
+    if (!encode) {
+        record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+        return UE5M3_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)k_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k_bytes};
+    cuuint32_t box[2] = {128u, box_rows};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        record_error_text("cuTensorMapEncodeTiled failed for packed codes");
+        return UE5M3_ERR_CUDA;
+    }
+    return UE5M3_OK;
+}
+
+}  // namespace ue5m3
+
+using namespace ue5m3;
+
+extern "C" size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K) {
+    if (rows <= 0 || K <= 0 || K % 64) return 0;
+    return (size_t)((rows + 127) / 128) * (size_t)(K / 64) * kSfAtomBytes;
+}
+
+extern "C" int ue5m3_pack_scales_ue4m3(const uint8_t* scales, int64_t rows, int64_t K, int block,
+                                       int two_d, int shift, uint8_t* sf_out, int* window_flag,
+                                       void* stream_v) {
+    if (!scales || !sf_out || !window_flag || rows <= 0 || K <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (block != 16 && block != 32) return UE5M3_ERR_BLOCK_SIZE;
+    if (K % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if (shift < -8 || shift > 8) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (((uintptr_t)sf_out % 16) != 0) return UE5M3_ERR_ALIGNMENT;
+    const int64_t row_tiles = (rows + 127) / 128, k_atoms = K / 64;
+    const int64_t total = row_tiles * k_atoms * 128;
+    int64_t want = (total + 255) / 256;
+    int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    pack_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        scales, rows, K / block, block, two_d ? block : 1, shift, reinterpret_cast<uint32_t*>(sf_out),
+        row_tiles, k_atoms, window_flag);
+    return check_launch();
+}
+
+extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const uint8_t* b_codes,
+                              const uint8_t* b_sf, int64_t M, int64_t N, int64_t K, int shift_sum,
+                              int snap, const float* alpha_dev, const void* bias, int bias_dtype,
+                              void* out, int out_dtype, int64_t ldo, int* status_dev, void* stream_v) {
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !out || M <= 0 || N <= 0 || K <= 0)
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (K % kFKMma) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if (out_dtype != UE5M3_DTYPE_BF16 && out_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (bias && bias_dtype != UE5M3_DTYPE_BF16 && bias_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (ldo < N || shift_sum < -100 || shift_sum > 100) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (((uintptr_t)a_codes % 16) || ((uintptr_t)b_codes % 16) || ((uintptr_t)a_sf % 16) || ((uintptr_t)b_sf % 16))
+        return UE5M3_ERR_ALIGNMENT;
+    if (((K / 2) % 16) != 0) return UE5M3_ERR_ALIGNMENT;  // TMA row pitch
+    if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    const int64_t tiles_m = (M + kFM - 1) / kFM, tiles_n = (N + kFN - 1) / kFN;
+    if (tiles_m * tiles_n > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+
+    CUtensorMap map_a, map_b;
+    int status = make_codes_map(&map_a, a_codes, M, K / 2, kFM);
+    if (status != UE5M3_OK) return status;
+    status = make_codes_map(&map_b, b_codes, N, K / 2, kFN);
+    if (status != UE5M3_OK) return status;
+
+    Fp4Params p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
+    p.rescale = ldexpf(1.0f, shift_sum);
+    p.alpha = alpha_dev; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
+    p.sfa = a_sf; p.sfb = b_sf;
+    p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
+
+    const size_t smem = (size_t)kFStages * kFStageBytes + sizeof(Fp4Barriers) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    const int64_t tiles = tiles_m * tiles_n;
+    const unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+    gemm_fp4_kernel<<<grid, kFThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(
+        map_a, map_b, p);
+    return check_launch();
+}

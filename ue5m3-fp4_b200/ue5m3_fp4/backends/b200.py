@@ -302,6 +302,68 @@ def gemm_issue_rz(
     return out
 
 
+_window_flags: dict[torch.device, Tensor] = {}
+
+
+def window_flag(device: torch.device) -> Tensor:
+    """Device int32[1] raised by pack_scales when a block scale does not fit the tensor core's
+    UE4M3 range at the chosen shift (the FP4 result is then invalid; use the BF16-issue GEMM)."""
+
+    flag = _window_flags.get(device)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _window_flags[device] = flag
+    return flag
+
+
+def scale_shift_for_target(scale_target: float) -> int:
+    """Power-of-two re-bias of a tensor's block scales: scales up to the target (with the
+    ties-to-even slack of one sixteenth) must not exceed UE4M3's maximum 448."""
+
+    return max(0, math.ceil(math.log2(scale_target / 448.0)))
+
+
+def pack_scales(scales: Tensor, *, rows: int, k: int, block_size: int, two_dimensional: bool, shift: int) -> Tensor:
+    """UE5M3 scale bytes of a K-major operand -> UE4M3 bytes in the tensor core's scale layout."""
+
+    _require_cuda(scales, "scales")
+    size = _native.load().ue5m3_packed_scales_bytes(rows, k)
+    if size == 0:
+        raise ValueError("K must be divisible by 64")
+    out = torch.empty(size, dtype=torch.uint8, device=scales.device)
+    with torch.cuda.device(scales.device):
+        status = _native.load().ue5m3_pack_scales_ue4m3(
+            scales.data_ptr(), rows, k, block_size, int(two_dimensional), shift, out.data_ptr(),
+            window_flag(scales.device).data_ptr(), _native.stream_ptr(scales.device),
+        )
+    _native.check(status, "ue5m3_pack_scales_ue4m3")
+    return out
+
+
+def gemm_fp4(
+    a_codes: Tensor, a_sf: Tensor, b_codes: Tensor, b_sf: Tensor, *, m: int, n: int, k: int, shift_sum: int,
+    snap: bool, alpha: Tensor | None = None, bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32,
+) -> Tensor:
+    """out[M,N] on packed E2M1 codes + packed scales with the FP4 block-scaled tensor cores."""
+
+    _require_cuda(a_codes, "a_codes")
+    if k % 64:
+        raise ValueError("K must be divisible by 64")
+    if a_codes.shape != (m, k // 2) or b_codes.shape != (n, k // 2):
+        raise ValueError("packed codes must be [rows, K/2] with the reduction axis contiguous")
+    out = torch.empty((m, n), dtype=out_dtype, device=a_codes.device)
+    with torch.cuda.device(a_codes.device):
+        status = _native.load().ue5m3_gemm_fp4(
+            a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(), m, n, k, shift_sum,
+            int(bool(snap)), _native.ptr(alpha), _native.ptr(bias),
+            _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
+            _native.dtype_code(out_dtype), n, gemm_status(a_codes.device).data_ptr(),
+            _native.stream_ptr(a_codes.device),
+        )
+    _native.check(status, "ue5m3_gemm_fp4")
+    return out
+
+
 def encoded_global_alpha(amax_a: Tensor, amax_b: Tensor, target_a: float, target_b: float) -> Tensor:
     """alpha = fl(amax_a*amax_b) / ((Ta*6)*(Tb*6)), evaluated with the very Torch
     expression of backends/triton/quantization.py:412-420 on the device scalars."""
