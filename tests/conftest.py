@@ -30,3 +30,11 @@ def gemm_golden():
 
 def golden_case_names(npz) -> list[str]:
     return sorted({key.split(".")[0] for key in npz.files})
+
+
+@pytest.fixture(params=["fp4", "bf16"])
+def gemm_path(request, monkeypatch):
+    """Run a test once per GEMM kernel: FP4 block-scaled tensor cores and the BF16-issue kernel."""
+
+    monkeypatch.setenv("UE5M3_GEMM_PATH", request.param)
+    return request.param

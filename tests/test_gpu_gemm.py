@@ -117,7 +117,7 @@ def _probe_case(b200, a, b, *, block, two_d, ta=448.0, tb=448.0, sr_a=False, ama
 
 @pytest.mark.parametrize("block", [16, 32])
 @pytest.mark.parametrize("m,k,n", [(35, 128, 69), (256, 512, 320), (128, 4096, 256)])
-def test_probe_matched_forward_distribution_is_bit_exact(b200, block, m, k, n):
+def test_probe_matched_forward_distribution_is_bit_exact(b200, gemm_path, block, m, k, n):
     g = torch.Generator().manual_seed(m * n)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
     w_t = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16).t().contiguous()
@@ -125,7 +125,7 @@ def test_probe_matched_forward_distribution_is_bit_exact(b200, block, m, k, n):
     assert np.array_equal(got, expect)
 
 
-def test_probe_matched_backward_distributions_are_bit_exact(b200):
+def test_probe_matched_backward_distributions_are_bit_exact(b200, gemm_path):
     g = torch.Generator().manual_seed(11)
     # dgrad: dY (Student-t, stochastic, held amax) x W (2-D tiles)
     dy = student_t_dy(192, 512, seed=3)
@@ -145,7 +145,7 @@ def test_probe_matched_backward_distributions_are_bit_exact(b200):
     assert np.array_equal(got, expect)
 
 
-def test_wide_dynamic_range_deviation_is_bounded(b200):
+def test_wide_dynamic_range_deviation_is_bounded(b200, gemm_path):
     """Per-block magnitudes spanning 2^-12..1: the exact issue sum no longer fits fp32, so
     the tensor core's intra-issue accumulation order shows.  The model's own sensitivity to
     that order is a few ulp of the largest partial; the result must stay within 4 such ulp."""
@@ -155,7 +155,7 @@ def test_wide_dynamic_range_deviation_is_bounded(b200):
     got, expect = _probe_case(b200, a, b, block=16, two_d=False)
     scale = np.abs(expect).max()
     assert np.all(np.abs(got - expect) <= 4 * np.spacing(np.float32(scale)) * 8)
-    print("wide-range: differing outputs", float((got != expect).mean()), "max ulp", int(ulp_distance(got, expect).max()))
+    print("wide-range", gemm_path, ": differing outputs", float((got != expect).mean()), "max ulp", int(ulp_distance(got, expect).max()))
 
 
 def test_headline_shape_sampled_tiles(b200):

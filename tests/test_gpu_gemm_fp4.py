@@ -1,0 +1,168 @@
+"""The FP4 block-scaled tensor-core GEMM (ue5m3_gemm_fp4) and its scale packer, through the
+C ABI: scale-factor layout against a numpy restatement, the UE4M3 window flag, bit-exactness
+against the oracle on packed operands, equality with the BF16-issue kernel, and the
+benchmark shape on sampled rows x columns."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_helpers import bf16_round, oracle_quantize, random_bits, student_t_dy, to_np, wide_range
+from oracle import ue5m3_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def b200():
+    from ue5m3_fp4.backends import b200 as module
+
+    assert module.available()
+    return module
+
+
+def _expected_scale_layout(scales: np.ndarray, rows: int, k: int, block: int, two_d: bool, shift: int) -> np.ndarray:
+    tiles, atoms = (rows + 127) // 128, k // 64
+    out = np.full((tiles, atoms, 512), 0x38, np.uint8)
+    group = block if two_d else 1
+    for r in range(rows):
+        tile, r1, r0 = r // 128, (r % 128) // 32, r % 32
+        for h in range(k // 16):
+            code = int(scales[r // group, h // (block // 16)]) - ((8 + shift) << 3)
+            out[tile, h // 4, r0 * 16 + r1 * 4 + h % 4] = min(max(code, 8), 0x7E)
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("rows,k,block,two_d,shift", [(128, 64, 16, False, 0), (300, 256, 16, False, 1),
+                                                      (200, 128, 32, False, 0), (160, 192, 16, True, 3),
+                                                      (96, 128, 32, True, 0)])
+def test_scale_packer_layout_and_rebias(b200, rows, k, block, two_d, shift):
+    g = torch.Generator().manual_seed(rows + k)
+    shape = ((rows + block - 1) // block if two_d else rows, k // block)
+    lo = (9 + shift) << 3
+    scales = torch.randint(lo, lo + 100, shape, generator=g, dtype=torch.int32).to(torch.uint8)
+    b200.window_flag(torch.device("cuda", 0)).zero_()
+    got = b200.pack_scales(scales.cuda(), rows=rows, k=k, block_size=block, two_dimensional=two_d, shift=shift)
+    assert np.array_equal(to_np(got), _expected_scale_layout(scales.numpy(), rows, k, block, two_d, shift))
+    assert int(b200.window_flag(got.device).item()) == 0
+
+
+def test_scale_window_flag(b200):
+    dev = torch.device("cuda", 0)
+    for code, expect in [(0x78, 0), ((9 << 3), 0), ((9 << 3) - 1, 1), ((23 << 3) | 6, 0), ((23 << 3) | 7, 1),
+                         (0xF7, 1), (1, 1)]:
+        b200.window_flag(dev).zero_()
+        scales = torch.full((128, 4), code, dtype=torch.uint8, device=dev)
+        b200.pack_scales(scales, rows=128, k=64, block_size=16, two_dimensional=False, shift=0)
+        assert int(b200.window_flag(dev).item()) == expect, hex(code)
+    b200.window_flag(dev).zero_()
+
+
+def _case(b200, a, bt, *, block, two_d, ta=448.0, tb=448.0, sr=False, held=1.0, seed=0):
+    """Quantize packed, run the FP4 GEMM and the BF16-issue GEMM, return both and the oracle."""
+
+    dev = torch.device("cuda", 0)
+    bits = random_bits(a.shape, seed, torch.uint8) if sr else None
+    amax_a = float(a.float().abs().max()) * held
+    amax_b = float(bt.float().abs().max())
+    ta_t = torch.tensor([amax_a], device=dev)
+    tb_t = torch.tensor([amax_b], device=dev)
+    b200.window_flag(dev).zero_()
+    op_a = b200.quantize_fp4_operand(a.cuda(), block_size=block, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=ta_t, scale_target=ta, rounding="StochasticFast" if sr else "TTE",
+                                     random_bits=None if bits is None else bits.cuda(),
+                                     shift_headroom=1 if held < 1.0 else 0)  # stale amax: scales exceed T
+    op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=block, blocking=b200.BLOCK_2D if two_d else b200.BLOCK_ROW,
+                                     transposed=False, tensor_amax=tb_t, scale_target=tb)
+    alpha = b200.encoded_global_alpha(ta_t, tb_t, ta, tb)
+    got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    qa = oracle_quantize(a.float(), block=block, blocking=o.BLOCK_ROW, amax=amax_a, target=ta, sr=sr, bits=bits)
+    qb = oracle_quantize(bt.float(), block=block, blocking=o.BLOCK_2D if two_d else o.BLOCK_ROW, amax=amax_b, target=tb)
+    expect = o.gemm_issue_rz(qa["encoded"], qb["encoded"], snap=True, alpha_value=float(alpha.item()))
+    return to_np(got), expect
+
+
+@pytest.mark.parametrize("block", [16, 32])
+@pytest.mark.parametrize("m,k,n", [(35, 128, 69), (128, 64, 256), (300, 320, 520), (256, 4096, 384)])
+def test_fp4_gemm_forward_distribution_bit_exact(b200, block, m, k, n):
+    g = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    got, expect = _case(b200, x, w, block=block, two_d=True)
+    assert np.array_equal(got, expect)
+
+
+def test_fp4_gemm_backward_distributions_bit_exact(b200):
+    g = torch.Generator().manual_seed(4)
+    dy = student_t_dy(192, 512, seed=3)
+    wt = (0.02 * torch.randn(384, 512, generator=g)).to(torch.bfloat16)
+    got, expect = _case(b200, dy, wt, block=16, two_d=True, sr=True, held=0.9, seed=5)
+    assert np.array_equal(got, expect)
+    dyt = (1e-4 * torch.randn(96, 256, generator=g)).to(torch.bfloat16)
+    xt = torch.relu(torch.randn(320, 256, generator=g)).square().to(torch.bfloat16)
+    got, expect = _case(b200, dyt, xt, block=32, two_d=False, ta=2048.0, sr=True, seed=6)
+    assert np.array_equal(got, expect)
+
+
+def test_fp4_gemm_wide_range_deviation(b200):
+    """Per-block magnitudes over 2^-12..1: issue sums no longer fit fp32 exactly, so the tensor
+    core's own accumulation is visible.  Stated bound: 32 ulp of the largest output."""
+
+    a = wide_range(128, 512, lo=-12, seed=21).to(torch.bfloat16)
+    b = wide_range(256, 512, lo=-12, seed=22).to(torch.bfloat16)
+    got, expect = _case(b200, a, b, block=16, two_d=False)
+    assert np.all(np.abs(got - expect) <= 32 * np.spacing(np.float32(np.abs(expect).max())))
+    print("fp4 wide-range: differing outputs", float((got != expect).mean()))
+
+
+def test_probe_matched_falls_back_when_a_scale_leaves_the_window(b200, monkeypatch):
+    from ue5m3_fp4.backends.triton import probe_matched_fp4_gemm
+
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(64, 128, generator=g)
+    a[:, 64:80] *= 2.0**-20  # one block per row far below the UE4M3 window
+    a = a.to(torch.bfloat16)
+    b = torch.randn(128, 96, generator=g).to(torch.bfloat16)
+    results = {}
+    for path in ("fp4", "bf16"):
+        monkeypatch.setenv("UE5M3_GEMM_PATH", path)
+        results[path] = probe_matched_fp4_gemm(a.cuda(), b.cuda(), block_size=16)
+    torch.cuda.synchronize()
+    assert torch.equal(results["fp4"], results["bf16"])
+    assert int(b200.window_flag(torch.device("cuda", 0)).item()) == 0  # consumed by the fallback
+    qa = oracle_quantize(a.float(), block=16, blocking=o.BLOCK_ROW, amax=float(a.float().abs().max()))
+    assert (qa["scale_codes"] < (9 << 3)).any()  # the case does leave the window
+
+
+def test_fp4_gemm_benchmark_shape_sampled(b200):
+    g = torch.Generator().manual_seed(0)
+    m, k, n = 8192, 4096, 21504
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    dev = torch.device("cuda", 0)
+    xc, wc = x.cuda(), w.cuda()
+    ax, aw = b200.tensor_amax(xc).reshape(1), b200.tensor_amax(wc).reshape(1)
+    b200.window_flag(dev).zero_()
+    op_a = b200.quantize_fp4_operand(xc, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=ax,
+                                     scale_target=448.0)
+    op_b = b200.quantize_fp4_operand(wc, block_size=16, blocking=b200.BLOCK_2D, transposed=False, tensor_amax=aw,
+                                     scale_target=448.0)
+    alpha = b200.encoded_global_alpha(ax, aw, 448.0, 448.0)
+    y = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8063, 8191] + list(range(3000, 3024)))
+    col_bands = [0, 240, 256, 10752, 21232, 21488, 7008, 7024]  # whole 16-row bands of W (2-D tiles)
+    cols = torch.cat([torch.arange(c, c + 16) for c in col_bands])
+    qx = oracle_quantize(x[rows].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
+    enc_w = np.concatenate([
+        oracle_quantize(w[c:c + 16].float(), block=16, blocking=o.BLOCK_2D, amax=float(aw.item()))["encoded"]
+        for c in col_bands
+    ])
+    expect = o.gemm_issue_rz(qx["encoded"], enc_w, snap=True, alpha_value=float(alpha.item()))
+    got = to_np(y[rows.cuda()][:, cols.cuda()])
+    assert np.array_equal(got, bf16_round(expect))

@@ -26,7 +26,7 @@ def _layer(in_f, out_f, *, bias, name="layers.0.mixer.up_proj", recipe=None, dty
     return layer
 
 
-def test_forward_equals_public_composition():
+def test_forward_equals_public_composition(gemm_path):
     from ue5m3_fp4.backends.triton import probe_matched_fp4_gemm
 
     layer = _layer(256, 192, bias=True)
@@ -44,7 +44,7 @@ def test_forward_equals_public_composition():
 
 
 @pytest.mark.parametrize("name,block", [("layers.45.mixer.down_proj", 16), ("layers.3.mixer.in_proj", 32)])
-def test_backward_matches_oracle_with_explicit_bits(monkeypatch, name, block):
+def test_backward_matches_oracle_with_explicit_bits(monkeypatch, gemm_path, name, block):
     import ue5m3_fp4.nn.linear as linear_module
     from ue5m3_fp4.recipe import UE5M3Recipe
 
@@ -68,6 +68,9 @@ def test_backward_matches_oracle_with_explicit_bits(monkeypatch, name, block):
     y = layer(x)
     y.backward(dy)
     torch.cuda.synchronize()
+    from ue5m3_fp4.backends import b200
+
+    b200.check_gemm_status(x.device)  # bounded waits and the FP4 scale window
     assert len(draws) == 2  # separate draws for dgrad and wgrad
 
     w = layer.weight.detach().float().cpu()

@@ -252,6 +252,13 @@ def gemm_status(device: torch.device) -> Tensor:
 def check_gemm_status(device: torch.device) -> None:
     """Synchronising check of the GEMM status words; raises if a wait expired."""
 
+    flag = _window_flags.get(device)
+    if flag is not None and int(flag.item()) != 0:
+        flag.zero_()
+        raise RuntimeError(
+            "a block scale fell outside the FP4 tensor core's scale window; the FP4 GEMM result is "
+            "invalid for that call - set UE5M3_GEMM_PATH=bf16 (issue-RZ kernel, no window)"
+        )
     words = gemm_status(device).tolist()
     if words[0]:
         gemm_status(device).zero_()
@@ -362,6 +369,65 @@ def gemm_fp4(
         )
     _native.check(status, "ue5m3_gemm_fp4")
     return out
+
+
+def gemm_path() -> str:
+    """"fp4" (block-scaled FP4 tensor cores, default) or "bf16" (issue-RZ kernel on encoded
+    bf16 operands), from the environment variable UE5M3_GEMM_PATH."""
+
+    import os
+
+    path = os.environ.get("UE5M3_GEMM_PATH", "fp4").strip().lower()
+    if path not in {"fp4", "bf16"}:
+        raise ValueError("UE5M3_GEMM_PATH must be 'fp4' or 'bf16'")
+    return path
+
+
+@dataclass(slots=True)
+class Fp4Operand:
+    """A K-major packed GEMM operand: codes [rows, K/2], scales in the tensor-core layout."""
+
+    codes: Tensor
+    scale_factors: Tensor
+    shift: int
+    rows: int
+    k: int
+
+
+def quantize_fp4_operand(
+    x: Tensor,
+    *,
+    block_size: int,
+    blocking: int,
+    transposed: bool,
+    tensor_amax: Tensor,
+    scale_target: float,
+    rounding: str | RoundingMode = RoundingMode.TIES_TO_EVEN,
+    random_bits: Tensor | None = None,
+    shift_headroom: int = 0,
+) -> Fp4Operand:
+    """Quantize ``x`` [R, C] into a packed K-major operand of the FP4 GEMM: reduction over C
+    (``transposed=False``: ROW or 2-D blocks) or over R (``transposed=True``: COL or 2-D
+    blocks, outputs written transposed)."""
+
+    packed = quantize_packed(
+        x, block_size=block_size, blocking=blocking, tensor_amax=tensor_amax, scale_target=scale_target,
+        rounding=rounding, random_bits=random_bits, packed=not transposed, packed_t=transposed,
+    )
+    rows, k = (x.shape[1], x.shape[0]) if transposed else (x.shape[0], x.shape[1])
+    codes = packed.codes_t if transposed else packed.codes
+    scales = packed.scales_t if transposed else packed.scales
+    shift = scale_shift_for_target(scale_target) + shift_headroom
+    sf = pack_scales(scales, rows=rows, k=k, block_size=block_size, two_dimensional=blocking == BLOCK_2D, shift=shift)
+    return Fp4Operand(codes, sf, shift, rows, k)
+
+
+def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor | None = None,
+                      bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
+    if a.k != b.k:
+        raise ValueError("a and b have incompatible K dimensions")
+    return gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
+                    shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype)
 
 
 def encoded_global_alpha(amax_a: Tensor, amax_b: Tensor, target_a: float, target_b: float) -> Tensor:
@@ -582,16 +648,29 @@ def probe_matched_fp4_gemm(
     bits_b = _resolve_bits(b, random_bits_b, rounding=mode_b, generator=generator, name="random_bits_b")
     amax_a = _resolve_amax(a, tensor_amax_a, name="tensor_amax_a", operand="a")
     amax_b = _resolve_amax(b, tensor_amax_b, name="tensor_amax_b", operand="b")
+    alpha = encoded_global_alpha(amax_a, amax_b, float(scale_target_a), float(scale_target_b))
+    blocking_b = BLOCK_2D if two_dimensional_b else BLOCK_COL
+    if gemm_path() == "fp4":
+        flag = window_flag(a.device)
+        flag.zero_()
+        op_a = quantize_fp4_operand(a, block_size=block_size, blocking=BLOCK_ROW, transposed=False,
+                                    tensor_amax=amax_a, scale_target=float(scale_target_a), rounding=mode_a,
+                                    random_bits=bits_a)
+        op_b = quantize_fp4_operand(b, block_size=block_size, blocking=blocking_b, transposed=True,
+                                    tensor_amax=amax_b, scale_target=float(scale_target_b), rounding=mode_b,
+                                    random_bits=bits_b)
+        if int(flag.item()) == 0:  # every block scale fits the tensor core's scale type
+            return gemm_fp4_operands(op_a, op_b, snap=snap_to_1_over_1024, alpha=alpha, out_dtype=torch.float32)
+        flag.zero_()
     enc_a = quantize_packed(
         a, block_size=block_size, blocking=BLOCK_ROW, tensor_amax=amax_a, scale_target=float(scale_target_a),
         rounding=mode_a, random_bits=bits_a, packed=False, fake_domain="encoded", fake_dtype=torch.bfloat16,
     ).fake
     enc_bt = quantize_packed(
-        b, block_size=block_size, blocking=BLOCK_2D if two_dimensional_b else BLOCK_COL, tensor_amax=amax_b,
+        b, block_size=block_size, blocking=blocking_b, tensor_amax=amax_b,
         scale_target=float(scale_target_b), rounding=mode_b, random_bits=bits_b, packed=False, packed_t=False,
         fake_domain="encoded", fake_dtype=torch.bfloat16, fake=False, fake_t=True,
     ).fake_t
-    alpha = encoded_global_alpha(amax_a, amax_b, float(scale_target_a), float(scale_target_b))
     return gemm_issue_rz(enc_a, enc_bt, snap=snap_to_1_over_1024, alpha=alpha, out_dtype=torch.float32)
 
 
@@ -599,13 +678,20 @@ __all__ = [
     "BLOCK_2D",
     "BLOCK_COL",
     "BLOCK_ROW",
+    "Fp4Operand",
     "PackedOperand",
     "available",
     "check_gemm_status",
     "dequantize_packed",
     "encoded_global_alpha",
     "fake_quantize_gemm_operands",
+    "gemm_fp4",
+    "gemm_fp4_operands",
     "gemm_issue_rz",
+    "gemm_path",
+    "pack_scales",
+    "quantize_fp4_operand",
+    "window_flag",
     "gemm_status",
     "issue_rz_bf16_gemm",
     "probe_matched_fp4_gemm",

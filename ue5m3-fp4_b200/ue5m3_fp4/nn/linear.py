@@ -126,9 +126,15 @@ class _OperandPlan:
     """Role -> (target, rounding) lookups of one module, resolved once per call."""
 
     def __init__(self, owner: UE5M3Linear) -> None:
+        from ue5m3_fp4.backends import b200
+
         self.recipe = owner.recipe
         self.name = owner.module_name
         self.block = owner.recipe.block_size
+        # FP4 tensor cores for the probe-matched backend unless the environment asks for the
+        # BF16-issue kernel; the torch control always multiplies encoded bf16 operands.
+        probe = owner.backend is LinearBackend.PROBE_MATCHED_TRITON
+        self.path = b200.gemm_path() if probe else "bf16"
 
     def target(self, role: str) -> float:
         return self.recipe.scale_target_for(role, self.name)
@@ -146,10 +152,11 @@ def _encode_k_major(
     reduce_over_rows: bool,
     two_dimensional: bool,
     bits: torch.Tensor | None = None,
-) -> torch.Tensor:
-    """Quantize ``tensor`` [R, C] for a GEMM and return its encoded bf16 values with the
-    reduction axis contiguous: [R, C] when the GEMM reduces over C, [C, R] when it
-    reduces over R (the quantizer writes the transpose itself)."""
+):
+    """Quantize ``tensor`` [R, C] into a GEMM operand with the reduction axis contiguous
+    ([R, C] when the GEMM reduces over C, [C, R] when it reduces over R; the quantizer writes
+    the transpose itself).  On the FP4 path the operand is packed codes + tensor-core scale
+    factors, on the BF16-issue path the encoded values ``p*s`` as bf16."""
 
     from ue5m3_fp4.backends import b200
 
@@ -160,6 +167,13 @@ def _encode_k_major(
         blocking = b200.BLOCK_2D
     else:
         blocking = b200.BLOCK_COL if reduce_over_rows else b200.BLOCK_ROW
+    if plan.path == "fp4":
+        # one binade of headroom: a held amax may lag the data between refreshes
+        return b200.quantize_fp4_operand(
+            tensor, block_size=plan.block, blocking=blocking, transposed=reduce_over_rows,
+            tensor_amax=reference.reshape(1), scale_target=plan.target(role), rounding=rounding,
+            random_bits=bits, shift_headroom=1,
+        )
     packed = b200.quantize_packed(
         tensor,
         block_size=plan.block,
@@ -179,8 +193,8 @@ def _encode_k_major(
 
 
 def _gemm(
-    a_enc: torch.Tensor,
-    bt_enc: torch.Tensor,
+    a_enc,
+    bt_enc,
     *,
     owner: UE5M3Linear,
     reference_a: torch.Tensor,
@@ -193,6 +207,8 @@ def _gemm(
     from ue5m3_fp4.backends import b200
 
     alpha = b200.encoded_global_alpha(reference_a.reshape(1), reference_b.reshape(1), target_a, target_b)
+    if isinstance(a_enc, b200.Fp4Operand):
+        return b200.gemm_fp4_operands(a_enc, bt_enc, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
     if owner.backend is LinearBackend.PROBE_MATCHED_TRITON:
         return b200.gemm_issue_rz(a_enc, bt_enc, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
     # torch control: same encoded operands, library FP32 matrix multiplication
