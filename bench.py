@@ -210,6 +210,7 @@ class HotPath:
         self.launches = 0
         self.gemm_events: list = []
         self.step_index = 0
+        self.path = b200.gemm_path()
 
     def refresh_activation_amax(self) -> None:
         """Sample max|X| on the device and MAX all-reduce it across the data-parallel ranks."""
@@ -225,21 +226,32 @@ class HotPath:
         if self.step_index % REFRESH_INTERVAL == 0:
             self.refresh_activation_amax()
         self.step_index += 1
-        xe = ops.quantize_packed(self.x, block_size=BLOCK, blocking=ops.BLOCK_ROW, tensor_amax=self.amax_x,
-                                 scale_target=TARGET, packed=False, fake_domain="encoded",
-                                 fake_dtype=torch.bfloat16).fake
-        we = ops.quantize_packed(self.w, block_size=BLOCK, blocking=ops.BLOCK_2D, tensor_amax=self.amax_w,
-                                 scale_target=TARGET, packed=False, packed_t=False, fake_domain="encoded",
-                                 fake_dtype=torch.bfloat16).fake
         alpha = ops.encoded_global_alpha(self.amax_x, self.amax_w, TARGET, TARGET)
+        if self.path == "fp4":
+            # packed codes + scale bytes, scales re-laid for the tensor core, FP4 MMA
+            xq = ops.quantize_fp4_operand(self.x, block_size=BLOCK, blocking=ops.BLOCK_ROW, transposed=False,
+                                          tensor_amax=self.amax_x, scale_target=TARGET)
+            wq = ops.quantize_fp4_operand(self.w, block_size=BLOCK, blocking=ops.BLOCK_2D, transposed=False,
+                                          tensor_amax=self.amax_w, scale_target=TARGET)
+            self.launches += 5
+        else:
+            xq = ops.quantize_packed(self.x, block_size=BLOCK, blocking=ops.BLOCK_ROW, tensor_amax=self.amax_x,
+                                     scale_target=TARGET, packed=False, fake_domain="encoded",
+                                     fake_dtype=torch.bfloat16).fake
+            wq = ops.quantize_packed(self.w, block_size=BLOCK, blocking=ops.BLOCK_2D, tensor_amax=self.amax_w,
+                                     scale_target=TARGET, packed=False, packed_t=False, fake_domain="encoded",
+                                     fake_dtype=torch.bfloat16).fake
+            self.launches += 3
         if time_gemm:
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-        y = ops.gemm_issue_rz(xe, we, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+        if self.path == "fp4":
+            y = ops.gemm_fp4_operands(xq, wq, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+        else:
+            y = ops.gemm_issue_rz(xq, wq, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
         if time_gemm:
             stop.record()
             self.gemm_events.append((start, stop))
-        self.launches += 3
         return y
 
     def step_e2e(self):
@@ -376,17 +388,26 @@ def run_ours(args) -> None:
     if rank == 0:
         quant = _quantize_headline(torch, b200, device, max(args.steps, 40), peaks)
         cpu = cpu_baseline() if world == 1 else None
-        peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        bf16_peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        fp4 = hot.path == "fp4"
+        # The FP4 kernel issues kind::mxf4nvf4 MMAs, four times the BF16 MMA rate of the same
+        # tensor core; its denominator is 4 x the measured cuBLAS BF16 figure (no FP4 peak is
+        # measured on this pool; the nominal dense FP4 figure is 9000 TFLOP/s).
+        peak_tf = 4.0 * bf16_peak if fp4 else bf16_peak
         achieved = flops_per_rank / gemm_s / 1e12
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xue5m3 codes as encoded bf16 -> fp32 RZ accumulate",
-            "data": "synthetic", "config": _config(world),
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": ("fp4 (e2m1 x ue5m3->ue4m3 block scales) tensor-core MMA, fp32 accumulate" if fp4
+                      else "fp4(e2m1)xue5m3 codes as encoded bf16 -> fp32 RZ accumulate"),
+            "data": "synthetic", "config": {**_config(world), "gemm_kernel": "gemm_fp4_kernel" if fp4 else "gemm_issue_rz_kernel"},
             "roofline": {
-                "kernel": "gemm_issue_rz_kernel", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
-                "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": None,
-                "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (burst {peaks['bf16_tflops']})",
+                "kernel": "gemm_fp4_kernel" if fp4 else "gemm_issue_rz_kernel", "bound": "tensor",
+                "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": None,
+                "peak_source": (f"4 x {peaks['source']} cuBLAS bf16 sustained ({bf16_peak}); nominal dense FP4 9000"
+                                if fp4 else f"{peaks['source']} cuBLAS bf16 sustained (burst {peaks['bf16_tflops']})"),
+                "frac_of_nominal_fp4_9000": achieved / 9000.0,
                 "algorithmic_flops_per_launch": flops_per_rank, "gemm_ms": gemm_s * 1e3,
             },
             "quantize": quant,
@@ -426,6 +447,18 @@ def run_case(args) -> None:
         alpha = b200.encoded_global_alpha(amax_a, amax_b, TARGET, TARGET)
         for _ in range(args.steps):
             b200.gemm_issue_rz(ae, be, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    elif args.case == "gemm-fp4-small":
+        m, n = 4096, 8192
+        a = torch.randn(m, K, generator=g).to(torch.bfloat16).to(device)
+        b = (0.02 * torch.randn(n, K, generator=g)).to(torch.bfloat16).to(device)
+        amax_a, amax_b = b200.tensor_amax(a).reshape(1), b200.tensor_amax(b).reshape(1)
+        qa = b200.quantize_fp4_operand(a, block_size=BLOCK, blocking=b200.BLOCK_ROW, transposed=False,
+                                       tensor_amax=amax_a, scale_target=TARGET)
+        qb = b200.quantize_fp4_operand(b, block_size=BLOCK, blocking=b200.BLOCK_2D, transposed=False,
+                                       tensor_amax=amax_b, scale_target=TARGET)
+        alpha = b200.encoded_global_alpha(amax_a, amax_b, TARGET, TARGET)
+        for _ in range(args.steps):
+            b200.gemm_fp4_operands(qa, qb, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
     else:
         z = torch.randn(M, K, generator=g)
         chi = torch.randn(3, M, K, generator=g).square().sum(0)
@@ -451,7 +484,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default=None, choices=["gemm-small", "quantize"],
+    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize"],
                         help="run one small kernel case for a profiler capture instead of the benchmark")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
