@@ -57,64 +57,95 @@ def _config(n_gpus: int) -> dict:
 # clocks sampled during the timed region
 # ---------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons polled through NVML every few milliseconds.
 
-    def __init__(self, device_index: int) -> None:
+    The timed region of the default run lasts tens of milliseconds, shorter than one
+    `nvidia-smi -lms` period, so the poll runs in-process.  `mark()` brackets the timed
+    region; the summary reports the samples inside the marks (all samples when there are
+    too few inside).
+    """
+
+    REASONS = {
+        "hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+        "sw_power_cap": 0x4,
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.002) -> None:
         self.device_index = device_index
-        self.lines: list[str] = []
-        self.proc = None
+        self.period_s = period_s
+        self.samples: list[tuple[float, int, float, int]] = []
+        self.marks: list[float] = []
+        self.handle = None
+        self.nvml = None
+        self.sm_max = None
         self.thread = None
+        self.stop_flag = threading.Event()
+
+    def _handle(self):
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        self.nvml = pynvml
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
-            )
-        except OSError:
-            self.proc = None
+            self.handle = self._handle()
+            self.sm_max = self.nvml.nvmlDeviceGetMaxClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)
+        except Exception:
+            self.handle = None
             return
 
-        def pump():
-            for line in self.proc.stdout:
-                self.lines.append(line.strip())
+        def poll():
+            nv, h = self.nvml, self.handle
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag.is_set():
+                try:
+                    self.samples.append((time.perf_counter(),
+                                         nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                         nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                         int(reasons_fn(h))))
+                except Exception:
+                    pass
+                time.sleep(self.period_s)
 
-        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread = threading.Thread(target=poll, daemon=True)
         self.thread.start()
 
+    def mark(self) -> None:
+        self.marks.append(time.perf_counter())
+
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, sm_max, power, reasons = [], [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
-            parts = [part.strip() for part in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                sm_max.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, value in zip(names, parts[5:9]):
-                if value.lower() == "active":
-                    reasons.add(name)
-        sm.sort()
+        if self.handle is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        rows = self.samples
+        window = "warm-up + timed region"
+        if len(self.marks) >= 2:
+            inside = [r for r in rows if self.marks[0] <= r[0] <= self.marks[-1]]
+            if len(inside) >= 3:
+                rows, window = inside, "timed region"
+        sm = sorted(r[1] for r in rows)
+        bits = 0
+        for r in rows:
+            bits |= r[3]
         return {
-            "sm_mhz": sm[len(sm) // 2] if sm else None,
-            "sm_max_mhz": max(sm_max) if sm_max else None,
-            "power_w_max": max(power) if power else None,
+            "sm_mhz": float(sm[len(sm) // 2]) if sm else None,
+            "sm_min_mhz": float(sm[0]) if sm else None,
+            "sm_max_mhz": float(self.sm_max) if self.sm_max else None,
+            "power_w_max": max((r[2] for r in rows), default=None),
             "samples": len(sm),
-            "reasons": sorted(reasons),
+            "window": window,
+            "reasons": sorted(name for name, bit in self.REASONS.items() if bits & bit),
         }
 
 
@@ -372,7 +403,9 @@ def run_ours(args) -> None:
         hot.step()
     hot.launches = 0
     hot.step_index = 0
+    sampler.mark()
     seconds = _timed(torch, dist, world, lambda: hot.step(time_gemm=True), args.steps)
+    sampler.mark()
     clocks = sampler.stop() if rank == 0 else None
     launches = hot.launches
     b200.check_gemm_status(device)

@@ -38,7 +38,9 @@ constexpr int kFN = 256;            // tile columns
 constexpr int kFKStage = 256;       // reduction elements per stage (128 bytes per row)
 constexpr int kFKMma = 64;          // reduction elements per MMA = one issue
 constexpr int kFStages = 4;
-constexpr int kFThreads = 320;
+constexpr int kFScaleWarps = 2;
+constexpr int kFScaleWarp0 = 10;
+constexpr int kFThreads = 32 * (kFScaleWarp0 + kFScaleWarps);  // producer, MMA, 8 epilogue, scale-copy warps
 constexpr int kFEpilogueWarps = 8;
 constexpr uint32_t kFTmemCols = 512;
 constexpr uint32_t kSfAtomBytes = 512;  // 128 rows x 4 scale bytes
@@ -70,6 +72,7 @@ struct Fp4Params {
 struct __align__(8) Fp4Barriers {
     unsigned long long full[kFStages];
     unsigned long long empty[kFStages];
+    unsigned long long sf_full[kFStages];
     unsigned long long tmem_full;
     unsigned long long tmem_empty;
     uint32_t tmem_base;
@@ -135,6 +138,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = 0; s < kFStages; ++s) {
             mbar_init(&bars->full[s], 1);
             mbar_init(&bars->empty[s], 1);
+            mbar_init(&bars->sf_full[s], kFScaleWarps);
         }
         mbar_init(&bars->tmem_full, 1);
         mbar_init(&bars->tmem_empty, kFEpilogueWarps);
@@ -203,30 +207,54 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 for (int j = 0; j < num_stages; ++j, ++g) {
                     const int s = g % kFStages;
-                    ok = mbar_wait(&bars->full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
+                    // scales of this stage are in TMEM, which also means its operands have landed
+                    ok = mbar_wait(&bars->sf_full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(smem + s * kFStageBytes);
                     const uint32_t sb = sa + kFBytesA;
-                    const uint32_t ssfa = sb + kFBytesB;
-                    const uint32_t ssfb = ssfa + kFBytesSfa;
                     const uint64_t desc_a = smem_desc_sw128(sa);
                     const uint64_t desc_b = smem_desc_sw128(sb);
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
                     for (int k = 0; k < issues_here; ++k) {
+                        const uint32_t slot = (uint32_t)(s * 4 + k);
+                        // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                        umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                 (j > 0 || k > 0) ? 1u : 0u, tmem_base + kTmemSfa + slot * 4,
+                                 tmem_base + kTmemSfb + slot * 8);
+                    }
+                    umma_commit(&bars->empty[s]);
+                }
+                if (ok) umma_commit(&bars->tmem_full);
+            }
+        }
+    } else if (warp >= kFScaleWarp0) {
+        // ---------------- scale atoms: shared memory -> TMEM, one slot ring entry per stage ----------------
+        // A landed stage (full) implies the MMAs that last read this stage's TMEM scale slots
+        // have completed, because the producer refilled the stage only after their commit.
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kFStages;
+                    ok = mbar_wait(&bars->full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 5, j);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t ssfa = smem_u32(smem + s * kFStageBytes) + kFBytesA + kFBytesB;
+                    const uint32_t ssfb = ssfa + kFBytesSfa;
+                    const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
+                    // the issuing thread is the bottleneck of these copies: split them over the warps
+                    for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
                         const uint32_t slot = (uint32_t)(s * 4 + k);
                         const uint32_t t_sfa = tmem_base + kTmemSfa + slot * 4;
                         const uint32_t t_sfb = tmem_base + kTmemSfb + slot * 8;
                         tmem_copy_sf(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
                         tmem_copy_sf(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
                         tmem_copy_sf(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
-                        // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
-                        umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                                 (j > 0 || k > 0) ? 1u : 0u, t_sfa, t_sfb);
                     }
-                    umma_commit(&bars->empty[s]);
+                    umma_commit(&bars->sf_full[s]);
                 }
-                if (ok) umma_commit(&bars->tmem_full);
             }
         }
     } else {
