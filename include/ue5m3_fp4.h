@@ -170,6 +170,21 @@ int ue5m3_pack_scales_ue4m3(const uint8_t *scales, int64_t rows, int64_t K, int 
                             int shift, uint8_t *sf_out, int *window_flag, void *stream);
 
 /*
+ * One-pass quantizer for an operand of ue5m3_gemm_fp4 whose reduction axis is the contiguous
+ * axis of x (blocking UE5M3_BLOCK_ROW or UE5M3_BLOCK_2D; cols = K, K % 64 == 0): same
+ * arithmetic as ue5m3_quantize (formats.py:350-457, backends/triton/quantization.py:34-200),
+ * writing codes [rows, K/2] and, when sf != NULL, the scales directly in the layout and UE4M3
+ * re-bias of ue5m3_pack_scales_ue4m3 (shift, window_flag as there).  scales (optional)
+ * receives the raw UE5M3 bytes as ue5m3_quantize would write them.  x 32-byte aligned, codes
+ * and sf 16-byte aligned.  Operands whose reduction axis is strided (UE5M3_BLOCK_COL,
+ * transposed outputs) go through ue5m3_quantize + ue5m3_pack_scales_ue4m3.
+ */
+int ue5m3_quantize_fp4_operand(const void *x, int dtype, int64_t rows, int64_t cols, int block,
+                               int blocking, const float *amax_dev, float target, int rounding,
+                               const void *bits, int bits_dtype, int shift, uint8_t *codes,
+                               uint8_t *sf, uint8_t *scales, int *window_flag, void *stream);
+
+/*
  * Probe-matched GEMM on PACKED operands with the FP4 block-scaled tensor cores:
  *   out[M,N] = epilogue( 2^shift_sum * sum over K=64 issues of (A codes x scales) . (B codes x scales) )
  * a_codes [M, K/2], b_codes [N, K/2] (E2M1 nibbles, reduction axis contiguous); a_sf, b_sf from

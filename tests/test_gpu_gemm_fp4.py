@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_helpers import bf16_round, oracle_quantize, random_bits, student_t_dy, to_np, wide_range
+from gpu_helpers import bf16_round, expect_packed, oracle_quantize, random_bits, student_t_dy, to_np, wide_range
 from oracle import ue5m3_oracle as o
 
 pytestmark = pytest.mark.gpu
@@ -166,3 +166,54 @@ def test_fp4_gemm_benchmark_shape_sampled(b200):
     expect = o.gemm_issue_rz(qx["encoded"], enc_w, snap=True, alpha_value=float(alpha.item()))
     got = to_np(y[rows.cuda()][:, cols.cuda()])
     assert np.array_equal(got, bf16_round(expect))
+
+
+@pytest.mark.parametrize("rows,k,block,blocking,sr,dtype", [
+    (128, 64, 16, "row", False, torch.bfloat16),
+    (300, 256, 16, "row", True, torch.bfloat16),
+    (77, 128, 32, "row", False, torch.float32),
+    (160, 192, 16, "2d", False, torch.bfloat16),
+    (203, 320, 16, "2d", True, torch.float32),
+    (96, 128, 32, "2d", False, torch.bfloat16),
+    (1000, 1024, 32, "2d", True, torch.bfloat16),
+])
+def test_one_pass_operand_quantizer_equals_quantize_then_pack(b200, rows, k, block, blocking, sr, dtype):
+    """ue5m3_quantize_fp4_operand (codes + UE4M3 atoms in one launch) against ue5m3_quantize
+    followed by ue5m3_pack_scales_ue4m3, and its codes and raw scales against the oracle."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(rows * 7 + k)
+    x = torch.randn(rows, k, generator=g)
+    x = x.to(torch.bfloat16).float() if dtype is torch.bfloat16 else x
+    bits = random_bits((rows, k), rows + k, torch.uint8) if sr else None
+    amax = torch.tensor([float(x.abs().max())], device=dev)
+    code = b200.BLOCK_ROW if blocking == "row" else b200.BLOCK_2D
+    rounding = "StochasticFast" if sr else "TTE"
+    xd = x.to(dtype).cuda()
+    bd = None if bits is None else bits.cuda()
+    b200.window_flag(dev).zero_()
+    shift = b200.scale_shift_for_target(448.0)
+    (op, raw) = b200._quantize_fp4_operand_fused(xd, block, code, amax, 448.0, rounding, bd, shift, want_scales=True)
+    two = b200.quantize_packed(xd, block_size=block, blocking=code, tensor_amax=amax, scale_target=448.0,
+                               rounding=rounding, random_bits=bd, packed=True, packed_t=False)
+    sf = b200.pack_scales(two.scales, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d", shift=shift)
+    assert int(b200.window_flag(dev).item()) == 0
+    assert torch.equal(op.codes, two.codes)
+    assert torch.equal(raw, two.scales)
+    assert torch.equal(op.scale_factors, sf)
+    ref = expect_packed(oracle_quantize(x, block=block, blocking=code, amax=float(amax.item()), target=448.0,
+                                        sr=sr, bits=bits))
+    assert np.array_equal(to_np(op.codes), ref["codes"])
+    assert np.array_equal(to_np(raw), ref["scales"])
+
+
+def test_one_pass_operand_quantizer_raises_the_window_flag(b200):
+    dev = torch.device("cuda", 0)
+    x = torch.ones(128, 64, dtype=torch.bfloat16, device=dev)
+    x[5, 3] = 3.0e4  # every other block's scale falls below the UE4M3 window
+    amax = torch.tensor([3.0e4], device=dev)
+    b200.window_flag(dev).zero_()
+    b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
+                              scale_target=448.0)
+    assert int(b200.window_flag(dev).item()) == 1
+    b200.window_flag(dev).zero_()

@@ -13,7 +13,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["abi.cu", "amax.cu", "quantize.cu", "gemm_sm100.cu", "gemm_fp4_sm100.cu"]
+SOURCES = ["abi.cu", "amax.cu", "quantize.cu", "quantize_operand.cu", "gemm_sm100.cu", "gemm_fp4_sm100.cu"]
 OUTPUT = HERE / "lib" / "libue5m3_b200.so"
 
 

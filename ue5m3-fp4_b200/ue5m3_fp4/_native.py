@@ -75,6 +75,8 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_packed_scales_bytes.argtypes = [i64, i64]
     lib.ue5m3_pack_scales_ue4m3.restype = i32
     lib.ue5m3_pack_scales_ue4m3.argtypes = [p, i64, i64, i32, i32, i32, p, p, p]
+    lib.ue5m3_quantize_fp4_operand.restype = i32
+    lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
     lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, i32, p, i32, i64, p, p]
     lib.ue5m3_test_e2m1_cvt.restype = i32
@@ -88,8 +90,15 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+launch_count = 0  # successful kernel-launching library calls of this process
+
+
 def check(status: int, what: str) -> None:
+    """Raise on a non-zero status; every entry point checked here launches one kernel."""
+
+    global launch_count
     if status == UE5M3_OK:
+        launch_count += 1
         return
     lib = load()
     text = lib.ue5m3_status_string(status).decode()

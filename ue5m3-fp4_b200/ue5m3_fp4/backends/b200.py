@@ -410,6 +410,11 @@ def quantize_fp4_operand(
     (``transposed=False``: ROW or 2-D blocks) or over R (``transposed=True``: COL or 2-D
     blocks, outputs written transposed)."""
 
+    shift = scale_shift_for_target(scale_target) + shift_headroom
+    if not transposed and blocking in (BLOCK_ROW, BLOCK_2D) and x.ndim == 2 and x.shape[1] % 64 == 0 \
+            and x.is_contiguous() and x.data_ptr() % 32 == 0:
+        return _quantize_fp4_operand_fused(x, block_size, blocking, tensor_amax, scale_target, rounding,
+                                           random_bits, shift)
     packed = quantize_packed(
         x, block_size=block_size, blocking=blocking, tensor_amax=tensor_amax, scale_target=scale_target,
         rounding=rounding, random_bits=random_bits, packed=not transposed, packed_t=transposed,
@@ -417,9 +422,50 @@ def quantize_fp4_operand(
     rows, k = (x.shape[1], x.shape[0]) if transposed else (x.shape[0], x.shape[1])
     codes = packed.codes_t if transposed else packed.codes
     scales = packed.scales_t if transposed else packed.scales
-    shift = scale_shift_for_target(scale_target) + shift_headroom
     sf = pack_scales(scales, rows=rows, k=k, block_size=block_size, two_dimensional=blocking == BLOCK_2D, shift=shift)
     return Fp4Operand(codes, sf, shift, rows, k)
+
+
+def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tensor_amax: Tensor,
+                                scale_target: float, rounding, random_bits: Tensor | None, shift: int,
+                                *, want_scales: bool = False):
+    """One launch: codes and tensor-core scale atoms (ue5m3_quantize_fp4_operand)."""
+
+    _require_cuda(x, "x")
+    if tensor_amax.device != x.device or tensor_amax.dtype is not torch.float32 or tensor_amax.numel() != 1:
+        raise ValueError("tensor_amax must be a one-element float32 tensor on the operand's device")
+    if block_size not in (16, 32):
+        raise ValueError("block_size must be 16 or 32")
+    mode = normalize_rounding(rounding)
+    stochastic = mode is RoundingMode.STOCHASTIC_8BIT_MIDPOINT
+    if stochastic:
+        if random_bits is None:
+            raise ValueError("stochastic rounding requires explicit random bits")
+        if random_bits.shape != x.shape or random_bits.device != x.device or not random_bits.is_contiguous():
+            raise ValueError("random bits must be contiguous, on the operand's device and of its shape")
+    elif random_bits is not None:
+        raise ValueError("random bits are only valid with stochastic rounding")
+    rows, k = x.shape
+    dev = x.device
+    lib = _native.load()
+    codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
+    scales = None
+    if want_scales:
+        scale_rows = rows if blocking == BLOCK_ROW else (rows + block_size - 1) // block_size
+        scales = torch.empty((scale_rows, k // block_size), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        status = lib.ue5m3_quantize_fp4_operand(
+            x.data_ptr(), _native.dtype_code(x.dtype), rows, k, block_size, blocking,
+            tensor_amax.data_ptr(), float(scale_target),
+            _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
+            _native.ptr(random_bits), _bits_code(random_bits), shift,
+            codes.data_ptr(), sf.data_ptr(), _native.ptr(scales),
+            window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+        )
+    _native.check(status, "ue5m3_quantize_fp4_operand")
+    operand = Fp4Operand(codes, sf, shift, rows, k)
+    return (operand, scales) if want_scales else operand
 
 
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor | None = None,
