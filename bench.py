@@ -508,6 +508,11 @@ def run_case(args) -> None:
             b200.quantize_packed(dy, block_size=BLOCK, blocking=b200.BLOCK_COL, tensor_amax=amax,
                                  rounding="StochasticFast", random_bits=bits, packed=False, packed_t=False,
                                  fake_domain="encoded", fake_dtype=torch.bfloat16, fake=False, fake_t=True)
+            b200.quantize_fp4_operand(dy, block_size=BLOCK, blocking=b200.BLOCK_ROW, transposed=False,
+                                      tensor_amax=amax, scale_target=TARGET, rounding="StochasticFast",
+                                      random_bits=bits, shift_headroom=1)
+            b200.quantize_fp4_operand(w, block_size=BLOCK, blocking=b200.BLOCK_2D, transposed=False,
+                                      tensor_amax=amax_w, scale_target=TARGET)
     torch.cuda.synchronize()
     b200.check_gemm_status(device)
     print("case", args.case, "done")

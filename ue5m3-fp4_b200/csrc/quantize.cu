@@ -29,7 +29,7 @@ namespace ue5m3 {
 // B = 16 a thread owns the whole block (no shuffle); with B = 32 two lanes share.
 // ---------------------------------------------------------------------------
 template <typename T, int B, int RMODE, int BITS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, RMODE == kRoundSr ? 3 : 4)
 quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __restrict__ amax_dev,
                     float six_t, const void* __restrict__ bits, uint2* __restrict__ codes,
                     uint8_t* __restrict__ scales, void* __restrict__ fake, int fake_dtype,
@@ -75,15 +75,21 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
                     for (int i = 0; i < 8; ++i) u[i] = v[k][h * 8 + i];
                     packed[h] = e2m1_pack8_hw(u);
                 }
+            } else if (RMODE == kRoundSr) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float u[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) u[i] = v[k][h * 8 + i];
+                    packed[h] = e2m1_pack8_sr(u, rb[k][2 * h], rb[k][2 * h + 1]);
+                }
             } else {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     packed[h] = 0u;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        uint32_t r14 = RMODE == kRoundSr ? r14_of(rb[k][(h * 8 + i) / 4], i & 3) : 0u;
-                        packed[h] += e2m1_nibble<RMODE == kRoundSr>(v[k][h * 8 + i], r14) * (1u << (4 * i));
-                    }
+                    for (int i = 0; i < 8; ++i)
+                        packed[h] += e2m1_nibble<false>(v[k][h * 8 + i], 0u) * (1u << (4 * i));
                 }
             }
             if (unit < nunits) {

@@ -115,15 +115,21 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                     for (int i = 0; i < 8; ++i) w[i] = v[u][h * 8 + i];
                     packed[u][h] = e2m1_pack8_hw(w);
                 }
+            } else if (kSr) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) w[i] = v[u][h * 8 + i];
+                    packed[u][h] = e2m1_pack8_sr(w, rb[u][2 * h], rb[u][2 * h + 1]);
+                }
             } else {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     packed[u][h] = 0u;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        uint32_t r14 = kSr ? r14_of(rb[u][(h * 8 + i) / 4], i & 3) : 0u;
-                        packed[u][h] += e2m1_nibble<kSr>(v[u][h * 8 + i], r14) * (1u << (4 * i));
-                    }
+                    for (int i = 0; i < 8; ++i)
+                        packed[u][h] += e2m1_nibble<false>(v[u][h * 8 + i], 0u) * (1u << (4 * i));
                 }
             }
         }

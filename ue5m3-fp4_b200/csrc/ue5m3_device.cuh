@@ -151,6 +151,99 @@ __device__ __forceinline__ void e2m1_unpack2_hw(uint32_t byte, float& lo, float&
     hi = f.y;
 }
 
+// ---- stochastic rounding of eight values at once -----------------------------------
+// Same rule as e2m1_index_sr, arranged so that the integer pipe does as little as possible
+// and nothing is selected per element.  With a = min(|u|, 6) two candidate indices are built:
+//  * H, exact for a >= 1: one byte permute builds (4 << 24) | (r << 16) | 0x8000
+//    = ((2r+1) << 15) + (4 << 24) from the packed random bytes; the TOP BYTE of
+//    4*bits(a) + that word is the index (2..7, nothing else set).
+//  * L = floor(fl(2a + mid)), exact for a < 2 (for a in [1, 2) the sum is exact and equals the
+//    carry rule; for a >= 2 it is >= 4).  mid = (2r+1) * 2^-9 comes from a second permute that
+//    builds the float 2^23 + r and one exact fma: (2^23 + r) * 2^-8 - (2^15 - 2^-9).  These
+//    run as packed fp32 instructions, two elements each; floor() is the low byte of
+//    RZ(z + 2^23).
+// Four H bytes and four L bytes are gathered into words and the index is, per byte,
+// L >= 4 ? H : L.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+    // default mode: a selector nibble with its top bit set replicates the sign bit of the
+    // selected byte over the result byte (the __byte_perm intrinsic drops that bit)
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+
+// t (top byte = H) and s (low byte = L, upper bytes 0x4B0000) of two elements
+__device__ __forceinline__ void e2m1_sr_candidates2(float u0, float u1, uint32_t rword, int k,
+                                                    uint32_t& t0, uint32_t& t1, uint32_t& s0,
+                                                    uint32_t& s1) {
+    const float a0 = fminf(fabsf(u0), 6.0f), a1 = fminf(fabsf(u1), 6.0f);
+    t0 = __float_as_uint(a0) * 4u + __byte_perm(rword, 0x00048000u, 0x6054u | ((uint32_t)k << 8));
+    t1 = __float_as_uint(a1) * 4u + __byte_perm(rword, 0x00048000u, 0x6054u | ((uint32_t)(k + 1) << 8));
+    const uint32_t m0 = __byte_perm(rword, 0x4B000000u, 0x7540u | (uint32_t)k);
+    const uint32_t m1 = __byte_perm(rword, 0x4B000000u, 0x7540u | (uint32_t)(k + 1));
+    asm("{\n"
+        ".reg .b64 m, a, z, c8, cm, c2, cb;\n"
+        "mov.b64 m, {%2, %3};\n"
+        "mov.b64 a, {%4, %5};\n"
+        "mov.b64 c8, {%6, %6};\n"
+        "mov.b64 cm, {%7, %7};\n"
+        "mov.b64 c2, {%8, %8};\n"
+        "mov.b64 cb, {%9, %9};\n"
+        "fma.rn.f32x2 m, m, c8, cm;\n"   // (2r+1) * 2^-9, exact
+        "fma.rn.f32x2 z, a, c2, m;\n"    // fl(2a + mid): the reference's own add where it rounds
+        "add.rz.f32x2 z, z, cb;\n"       // 2^23 + floor(z)
+        "mov.b64 {%0, %1}, z;\n"
+        "}\n"
+        : "=r"(s0), "=r"(s1)
+        : "r"(m0), "r"(m1), "f"(a0), "f"(a1), "f"(0.00390625f), "f"(-32767.998046875f), "f"(2.0f),
+          "f"(8388608.0f));
+}
+
+// top bytes of four words -> one word (w0's in the lowest byte)
+__device__ __forceinline__ uint32_t gather_top_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+    return __byte_perm(__byte_perm(w0, w1, 0x0073u), __byte_perm(w2, w3, 0x0073u), 0x5410u);
+}
+
+// low bytes of four words 0x4B0000xx -> one word, by multiply-adds (s0's in the lowest byte)
+__device__ __forceinline__ uint32_t gather_low_bytes_of_magic(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3) {
+    uint32_t acc = s3 * 0x1000000u + 0xB5000000u;  // cancels the 0x4B that s0 leaves in the top byte
+    acc = s2 * 0x10000u + acc;
+    acc = s1 * 0x100u + acc;
+    return acc + s0;
+}
+
+// per word 0xFF if its sign bit is set, else 0x00 (w0's in the lowest byte)
+__device__ __forceinline__ uint32_t gather_sign_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+    return prmt(prmt(w0, w1, 0x00FBu), prmt(w2, w3, 0x00FBu), 0x5410u);
+}
+
+// per byte: l >= 4 ? h : l   (l <= 12 in every byte)
+__device__ __forceinline__ uint32_t select_index_bytes(uint32_t h, uint32_t l) {
+    const uint32_t biased = l + 0x7C7C7C7Cu;  // bit 7 of a byte set iff l >= 4
+    const uint32_t mask = prmt(biased, biased, 0xBA98u);
+    return (h & mask) | (l & ~mask);
+}
+
+// Eight scaled inputs -> eight packed nibbles (element 0 lowest), 8-bit-midpoint stochastic
+// rounding; r03 / r47 hold the random bytes of elements 0..3 / 4..7.
+__device__ __forceinline__ uint32_t e2m1_pack8_sr(const float (&u)[8], uint32_t r03, uint32_t r47) {
+    uint32_t t[8], s[8];
+#pragma unroll
+    for (int i = 0; i < 8; i += 2)
+        e2m1_sr_candidates2(u[i], u[i + 1], i < 4 ? r03 : r47, i & 3, t[i], t[i + 1], s[i], s[i + 1]);
+    const uint32_t even = select_index_bytes(gather_top_bytes(t[0], t[2], t[4], t[6]),
+                                             gather_low_bytes_of_magic(s[0], s[2], s[4], s[6]));
+    const uint32_t odd = select_index_bytes(gather_top_bytes(t[1], t[3], t[5], t[7]),
+                                            gather_low_bytes_of_magic(s[1], s[3], s[5], s[7]));
+    const uint32_t magnitude = even + odd * 16u;  // indices <= 7: no carry between nibbles
+    const uint32_t se = gather_sign_bytes(__float_as_uint(u[0]), __float_as_uint(u[2]),
+                                          __float_as_uint(u[4]), __float_as_uint(u[6]));
+    const uint32_t so = gather_sign_bytes(__float_as_uint(u[1]), __float_as_uint(u[3]),
+                                          __float_as_uint(u[5]), __float_as_uint(u[7]));
+    const uint32_t signs = (se & 0x0F0F0F0Fu) | (so & 0xF0F0F0F0u);
+    return magnitude | (signs & 0x88888888u);
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
     return __uint_as_float(bits16 << 16);
 }
