@@ -217,3 +217,19 @@ def test_one_pass_operand_quantizer_raises_the_window_flag(b200):
                               scale_target=448.0)
     assert int(b200.window_flag(dev).item()) == 1
     b200.window_flag(dev).zero_()
+
+
+@pytest.mark.parametrize("m,k,n,block,two_d", [(256, 256, 256, 16, True), (35, 128, 69, 16, True),
+                                               (640, 4096, 768, 16, True), (300, 576, 520, 32, False)])
+def test_cta_pair_kernel_is_bit_equal_to_the_single_cta_kernel_and_the_oracle(b200, monkeypatch, m, k, n, block, two_d):
+    """UE5M3_FP4_CTA_PAIR=1 selects the cluster-of-two kernel (256 x 256 tiles, cta_group::2)."""
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    bt = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    monkeypatch.setenv("UE5M3_FP4_CTA_PAIR", "1")
+    pair, expect = _case(b200, a, bt, block=block, two_d=two_d)
+    monkeypatch.setenv("UE5M3_FP4_CTA_PAIR", "0")
+    single, _ = _case(b200, a, bt, block=block, two_d=two_d)
+    assert np.array_equal(pair, single)
+    assert np.array_equal(pair, expect)

@@ -105,6 +105,71 @@ __host__ __device__ constexpr uint32_t make_idesc_fp4(int m, int n) {
     return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Epilogue arithmetic and stores of one thread: 128 accumulator values of one output row
+// (columns [tile_n * 256 + h * 128, + 128)): rescale by 2^shift, snap, alpha, bias, cast.
+__device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t (&v)[4][32], long long row,
+                                              int tile_n, int h, float alpha) {
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
+        if (col0 >= p.N) continue;
+        float c[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float x = __fmul_rn(__uint_as_float(v[chunk][i]), p.rescale);
+            if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
+            if (p.alpha) x = __fmul_rn(x, alpha);
+            c[i] = x;
+        }
+        if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                int col = col0 + i;
+                if (col < p.N) {
+                    float bv = p.bias_dtype == UE5M3_DTYPE_BF16
+                                   ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
+                                   : static_cast<const float*>(p.bias)[col];
+                    c[i] = __fadd_rn(c[i], bv);
+                }
+            }
+        }
+        if (p.out_dtype == UE5M3_DTYPE_BF16) {
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+            const bool vec = (p.ldo % 8) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                if (vec && col0 + i + 8 <= p.N) {
+                    uint4 w;
+                    uint32_t hb[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        hb[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + e]));
+                    w.x = hb[0] | (hb[1] << 16); w.y = hb[2] | (hb[3] << 16);
+                    w.z = hb[4] | (hb[5] << 16); w.w = hb[6] | (hb[7] << 16);
+                    *reinterpret_cast<uint4*>(out + i) = w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (col0 + i + e < p.N) out[i + e] = __float2bfloat16_rn(c[i + e]);
+                }
+            }
+        } else {
+            float* out = static_cast<float*>(p.out) + row * p.ldo + col0;
+            const bool vec = (p.ldo % 4) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                if (vec && col0 + i + 4 <= p.N) {
+                    *reinterpret_cast<float4*>(out + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (col0 + i + e < p.N) out[i + e] = c[i + e];
+                }
+            }
+        }
+    }
+}
+
 // tile index -> (tile_m, tile_n): groups of 8 tile rows sweep the tile columns together
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tile_m, int& tile_n) {
     constexpr int kGroupM = 8;
@@ -281,65 +346,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
             const long long row = (long long)tile_m * kFM + q * 32 + lane;
             if (row >= p.M) continue;
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) {
-                const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
-                if (col0 >= p.N) continue;
-                float c[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __fmul_rn(__uint_as_float(v[chunk][i]), p.rescale);
-                    if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
-                    if (p.alpha) x = __fmul_rn(x, alpha);
-                    c[i] = x;
-                }
-                if (p.bias) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        int col = col0 + i;
-                        if (col < p.N) {
-                            float bv = p.bias_dtype == UE5M3_DTYPE_BF16
-                                           ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
-                                           : static_cast<const float*>(p.bias)[col];
-                            c[i] = __fadd_rn(c[i], bv);
-                        }
-                    }
-                }
-                if (p.out_dtype == UE5M3_DTYPE_BF16) {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
-                    const bool vec = (p.ldo % 8) == 0 && ((uintptr_t)p.out % 16) == 0;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        if (vec && col0 + i + 8 <= p.N) {
-                            uint4 w;
-                            uint32_t hb[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                hb[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + e]));
-                            w.x = hb[0] | (hb[1] << 16); w.y = hb[2] | (hb[3] << 16);
-                            w.z = hb[4] | (hb[5] << 16); w.w = hb[6] | (hb[7] << 16);
-                            *reinterpret_cast<uint4*>(out + i) = w;
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (col0 + i + e < p.N) out[i + e] = __float2bfloat16_rn(c[i + e]);
-                        }
-                    }
-                } else {
-                    float* out = static_cast<float*>(p.out) + row * p.ldo + col0;
-                    const bool vec = (p.ldo % 4) == 0 && ((uintptr_t)p.out % 16) == 0;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        if (vec && col0 + i + 4 <= p.N) {
-                            *reinterpret_cast<float4*>(out + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col0 + i + e < p.N) out[i + e] = c[i + e];
-                        }
-                    }
-                }
-            }
+            fp4_store_row(p, v, row, tile_n, h, alpha);
         }
     }
 
@@ -348,6 +355,247 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kFTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant (cluster of two CTAs, tcgen05 cta_group::2): one 256 x 256 output tile per
+// pair.  Each CTA loads its own 128 rows of A and its own half (128 rows) of the 256-column B
+// tile, so a K=256 stage moves 38 KiB per CTA instead of 54 KiB and every MMA reads 8 KiB of
+// shared memory per CTA instead of 12 KiB.  The leader CTA (rank 0) issues the scale copies,
+// the MMAs and the commits for both; every load of both CTAs reports to the leader's `full`
+// barrier (plain TMA loads with cta_group::2, no multicast).  Each CTA drains its own 128
+// accumulator rows.
+// ---------------------------------------------------------------------------------------
+constexpr int kPM = 256;
+constexpr int kPStages = 5;
+constexpr uint32_t kPBytesA = 128 * kFKStage / 2;
+constexpr uint32_t kPBytesB = 128 * kFKStage / 2;
+constexpr uint32_t kPStageBytes = kPBytesA + kPBytesB + kFBytesSfa + kFBytesSfb;
+constexpr uint32_t kPTmemSfa = 256;                      // kPStages * 4 slots x 4 columns
+constexpr uint32_t kPTmemSfb = kPTmemSfa + kPStages * 16;  // kPStages * 4 slots x 8 columns
+static_assert(kPTmemSfb + kPStages * 32 <= 512, "TMEM columns");
+
+struct __align__(8) Fp4PairBarriers {
+    unsigned long long full[kPStages];     // leader's: bytes of both CTAs
+    unsigned long long empty[kPStages];    // each CTA's own, signalled by the leader's commits
+    unsigned long long sf_full[kPStages];  // leader's
+    unsigned long long tmem_full;          // each CTA's own
+    unsigned long long tmem_empty;         // leader's: epilogue warps of both CTAs
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void umma_fp4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// the copy runs in both CTAs, each from its own shared memory into its own TMEM
+__device__ __forceinline__ void tmem_copy_sf_pair(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// pair tile index -> (tile_m, tile_n): groups of 4 tile rows (1024 rows of A) sweep the columns
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tile_m, int& tile_n) {
+    constexpr int kGroupM = 4;
+    const int tiles_per_group = kGroupM * tiles_n;
+    const int group = tile / tiles_per_group;
+    const int first_m = group * kGroupM;
+    const int group_m = (tiles_m - first_m) < kGroupM ? (tiles_m - first_m) : kGroupM;
+    tile_m = first_m + (tile % tiles_per_group) % group_m;
+    tile_n = (tile % tiles_per_group) / group_m;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1)
+gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                     const Fp4Params p) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    Fp4PairBarriers* bars = reinterpret_cast<Fp4PairBarriers*>(smem + kPStages * kPStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int num_issues = p.K / kFKMma;
+    const int num_stages = (num_issues + 3) / 4;
+    const int sf_k = num_issues;
+    const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+    const int where_base = 10 + 10 * (int)rank;   // wait sites reported as 11..15 (leader), 21..25 (peer)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+            mbar_init(&bars->sf_full[s], kFScaleWarps);
+        }
+        mbar_init(&bars->tmem_full, 1);
+        mbar_init(&bars->tmem_empty, 2 * kFEpilogueWarps);
+        bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc_pair(&bars->tmem_base, kFTmemCols);
+    tcgen05_fence_before();
+    cluster_sync_all();  // both CTAs' barriers exist before anything signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *((volatile uint32_t*)&bars->tmem_base);
+    const bool dead = *((volatile int*)&bars->abort_flag) != 0;
+
+    if (dead) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        // ---------------- producer (both CTAs): own A rows, own B half, own scale atoms ----------------
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                int tile_m, tile_n;
+                pair_tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+                const int m0 = tile_m * kPM + (int)rank * 128;
+                const int n0 = tile_n * kFN + (int)rank * 128;
+                const int sfa_row = (tile_m * 2 + (int)rank) * sf_k;
+                const int sfb_row = (tile_n * 2) * sf_k;
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kPStages;
+                    const uint32_t use = g / kPStages;
+                    if (use > 0) {
+                        ok = mbar_wait_cluster(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status,
+                                               where_base + 1, j);
+                        if (!ok) break;
+                    }
+                    unsigned char* sa = smem + s * kPStageBytes;
+                    unsigned char* sb = sa + kPBytesA;
+                    unsigned char* ssfa = sb + kPBytesB;
+                    unsigned char* ssfb = ssfa + kFBytesSfa;
+                    // out-of-range rows / atoms are zero-filled and still counted, so the byte
+                    // count of a stage is constant
+                    if (leader) mbar_arrive_expect_tx(&bars->full[s], 2 * kPStageBytes);
+                    const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[s]), 0);
+                    tma_load_2d_pair(sa, &map_a, full_leader, j * (kFKStage / 2), m0);
+                    tma_load_2d_pair(sb, &map_b, full_leader, j * (kFKStage / 2), n0);
+                    tma_load_2d_pair(ssfa, &map_sfa, full_leader, 0, sfa_row + 4 * j);
+                    tma_load_2d_pair(ssfb, &map_sfb, full_leader, 0, sfb_row + 4 * j);
+                    tma_load_2d_pair(ssfb + 4 * kSfAtomBytes, &map_sfb, full_leader, 0, sfb_row + sf_k + 4 * j);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue (leader only) ----------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_idesc_fp4(kPM, kFN);
+            const uint32_t empty_peer0 = map_to_cta(smem_u32(&bars->empty[0]), 1);
+            const uint32_t tmem_full_peer = map_to_cta(smem_u32(&bars->tmem_full), 1);
+            uint32_t g = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+                if (it > 0) {  // both CTAs must have drained the previous tile
+                    ok = mbar_wait_cluster(&bars->tmem_empty, (it - 1) & 1, &bars->abort_flag, p.status,
+                                           where_base + 2, it);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                }
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kPStages;
+                    ok = mbar_wait(&bars->sf_full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
+                                   where_base + 3, j);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * kPStageBytes);
+                    const uint32_t sb = sa + kPBytesA;
+                    const uint64_t desc_a = smem_desc_sw128(sa);
+                    const uint64_t desc_b = smem_desc_sw128(sb);
+                    const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
+                    for (int k = 0; k < issues_here; ++k) {
+                        const uint32_t slot = (uint32_t)(s * 4 + k);
+                        umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                      (j > 0 || k > 0) ? 1u : 0u, tmem_base + kPTmemSfa + slot * 4,
+                                      tmem_base + kPTmemSfb + slot * 8);
+                    }
+                    // the stage is free in both CTAs once these MMAs have completed
+                    umma_commit_pair(smem_u32(&bars->empty[s]));
+                    umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
+                }
+                if (ok) {
+                    umma_commit_pair(smem_u32(&bars->tmem_full));
+                    umma_commit_pair(tmem_full_peer);
+                }
+            }
+        }
+    } else if (warp >= kFScaleWarp0) {
+        // ---------------- scale atoms shared -> TMEM in both CTAs (issued by the leader) ----------------
+        if (lane == 0 && leader) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                for (int j = 0; j < num_stages; ++j, ++g) {
+                    const int s = g % kPStages;
+                    ok = mbar_wait_cluster(&bars->full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
+                                           where_base + 5, j);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t ssfa = smem_u32(smem + s * kPStageBytes) + kPBytesA + kPBytesB;
+                    const uint32_t ssfb = ssfa + kFBytesSfa;
+                    const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
+                    for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
+                        const uint32_t slot = (uint32_t)(s * 4 + k);
+                        const uint32_t t_sfa = tmem_base + kPTmemSfa + slot * 4;
+                        const uint32_t t_sfb = tmem_base + kPTmemSfb + slot * 8;
+                        tmem_copy_sf_pair(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
+                        tmem_copy_sf_pair(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
+                        tmem_copy_sf_pair(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                    }
+                    umma_commit_pair(smem_u32(&bars->sf_full[s]));
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): own 128 accumulator rows ----------------
+        const int q = warp & 3;
+        const int h = (warp - 2) >> 2;
+        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        const uint32_t tmem_empty_leader = map_to_cta(smem_u32(&bars->tmem_empty), 0);
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+            int tile_m, tile_n;
+            pair_tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+            bool ok = mbar_wait_cluster(&bars->tmem_full, it & 1, &bars->abort_flag, p.status, where_base + 4, it);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
+            uint32_t v[4][32];
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) tmem_load_32_async(taddr + chunk * 32, v[chunk]);
+            tmem_wait_ld();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tmem_empty_leader);
+
+            const long long row = (long long)tile_m * kPM + (long long)rank * 128 + q * 32 + lane;
+            if (row >= p.M) continue;
+            fp4_store_row(p, v, row, tile_n, h, alpha);
+        }
+    }
+
+    // nobody leaves while the other CTA may still read its shared memory or signal its barriers
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, kFTmemCols);
     }
 }
 
@@ -431,6 +679,36 @@ static int make_codes_map(CUtensorMap* map, const void* base, int64_t rows, int6
     return UE5M3_OK;
 }
 
+// scale atoms as a 2-D map: 128 words per atom, box = four consecutive atoms, no swizzle
+static int make_sf_map(CUtensorMap* map, const void* base, int64_t atoms) {
+    PFN_cuTensorMapEncodeTiled_v12000 encode = fp4_encode_fn();
+    if (!encode) {
+        record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+        return UE5M3_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {128u, (cuuint64_t)atoms};
+    cuuint64_t strides[1] = {512u};
+    cuuint32_t box[2] = {128u, 4u};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        record_error_text("cuTensorMapEncodeTiled failed for scale atoms");
+        return UE5M3_ERR_CUDA;
+    }
+    return UE5M3_OK;
+}
+
+// The CTA-pair kernel is selected by UE5M3_FP4_CTA_PAIR=1 in the environment (read at every
+// call).  It is bit-equal to the single-CTA kernel and moves a third less data per SM, but on
+// the benchmark shape it is the slower of the two (0.39 ms against 0.37 ms): both are bound by
+// the issue rate of the tcgen05 instruction stream, not by data movement.
+static bool use_cta_pair() {
+    const char* e = getenv("UE5M3_FP4_CTA_PAIR");
+    return e && e[0] == '1';
+}
+
 }  // namespace ue5m3
 
 using namespace ue5m3;
@@ -472,13 +750,15 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
         return UE5M3_ERR_ALIGNMENT;
     if (((K / 2) % 16) != 0) return UE5M3_ERR_ALIGNMENT;  // TMA row pitch
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
-    const int64_t tiles_m = (M + kFM - 1) / kFM, tiles_n = (N + kFN - 1) / kFN;
+    const bool pair = use_cta_pair();
+    const int64_t tile_rows = pair ? kPM : kFM;
+    const int64_t tiles_m = (M + tile_rows - 1) / tile_rows, tiles_n = (N + kFN - 1) / kFN;
     if (tiles_m * tiles_n > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
 
     CUtensorMap map_a, map_b;
-    int status = make_codes_map(&map_a, a_codes, M, K / 2, kFM);
+    int status = make_codes_map(&map_a, a_codes, M, K / 2, 128);
     if (status != UE5M3_OK) return status;
-    status = make_codes_map(&map_b, b_codes, N, K / 2, kFN);
+    status = make_codes_map(&map_b, b_codes, N, K / 2, pair ? 128 : kFN);
     if (status != UE5M3_OK) return status;
 
     Fp4Params p;
@@ -488,13 +768,46 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
     p.sfa = a_sf; p.sfb = b_sf;
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
+    const int64_t tiles = tiles_m * tiles_n;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    if (pair) {
+        CUtensorMap map_sfa, map_sfb;
+        status = make_sf_map(&map_sfa, a_sf, ((M + 127) / 128) * (K / 64));
+        if (status != UE5M3_OK) return status;
+        status = make_sf_map(&map_sfb, b_sf, ((N + 127) / 128) * (K / 64));
+        if (status != UE5M3_OK) return status;
+        const size_t smem = (size_t)kPStages * kPStageBytes + sizeof(Fp4PairBarriers) + 1024;
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        static int max_pairs[64] = {0};
+        int device = 0;
+        cudaGetDevice(&device);
+        if (device >= 0 && device < 64 && max_pairs[device] == 0) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+            config.blockDim = dim3(kFThreads);
+            config.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attribute;
+            attribute.id = cudaLaunchAttributeClusterDimension;
+            attribute.val.clusterDim.x = 2; attribute.val.clusterDim.y = 1; attribute.val.clusterDim.z = 1;
+            config.attrs = &attribute;
+            config.numAttrs = 1;
+            int clusters = 0;
+            e = cudaOccupancyMaxActiveClusters(&clusters, gemm_fp4_pair_kernel, &config);
+            if (e != cudaSuccess) return record_cuda_error(e);
+            max_pairs[device] = clusters > 0 ? clusters : 1;
+        }
+        const int64_t resident = (device >= 0 && device < 64) ? max_pairs[device] : sm_count() / 2;
+        const unsigned pairs = (unsigned)(tiles < resident ? tiles : resident);
+        gemm_fp4_pair_kernel<<<2 * pairs, kFThreads, smem, stream>>>(map_a, map_b, map_sfa, map_sfb, p);
+        return check_launch();
+    }
 
     const size_t smem = (size_t)kFStages * kFStageBytes + sizeof(Fp4Barriers) + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return record_cuda_error(e);
-    const int64_t tiles = tiles_m * tiles_n;
     const unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-    gemm_fp4_kernel<<<grid, kFThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(
-        map_a, map_b, p);
+    gemm_fp4_kernel<<<grid, kFThreads, smem, stream>>>(map_a, map_b, p);
     return check_launch();
 }

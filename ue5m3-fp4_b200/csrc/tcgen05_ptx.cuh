@@ -162,6 +162,99 @@ __device__ __forceinline__ uint64_t smem_desc_noswizzle_32x16(uint32_t smem_addr
     return desc;
 }
 
+// ---- CTA pairs (cluster of two, tcgen05 cta_group::2) ----------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+
+// arrive on an mbarrier of any CTA of the cluster (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(unsigned long long* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// mbar_wait with cluster-scope acquire, for barriers that the peer CTA (its threads, its TMA
+// unit or the leader's commits) arrives on
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned long long* bar, uint32_t parity, int* abort_flag,
+                                                  int* status, int where, int iter) {
+    const long long start = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int spin = 0; spin < 32; ++spin)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*((volatile int*)abort_flag)) return false;
+        if (clock64() - start > kWaitBudgetClocks) {
+            *((volatile int*)abort_flag) = 1;
+            if (status) {
+                if (atomicCAS(&status[0], 0, 1) == 0) {
+                    status[1] = where;
+                    status[2] = iter;
+                    status[3] = (int)blockIdx.x;
+                }
+            }
+            return false;
+        }
+    }
+}
+
+// every thread of both CTAs of the cluster
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();  // the barrier instructions are warp-aligned: reconverge first
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// 2-D tiled TMA load into this CTA's shared memory whose completion is counted on an mbarrier
+// given by shared::cluster address (the pair leader's); no multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// arrives (on the mbarrier at a shared::cluster address) once every tcgen05 operation issued so
+// far by this thread has completed in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+
 // round-half-even to an integer (torch.round), full-rate float ops only
 __device__ __forceinline__ float rint_rne(float v) {
     float a = fabsf(v);
