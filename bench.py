@@ -372,6 +372,31 @@ def _quantize_headline(torch, ops, device, steps: int, peaks: dict) -> dict:
     }
 
 
+def _library_fp4_reference(torch, device):
+    """cuBLASLt's NVFP4 GEMM (torch._scaled_mm, block-16 UE4M3 scales) on the benchmark shape,
+    random codes: a measured library figure beside the roofline (this pool's peak file has no FP4
+    entry).  Runs after the timed regions; returns TFLOP/s or None when the build lacks the path."""
+
+    try:
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=device).view(torch.float4_e2m1fn_x2)
+        b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device).view(torch.float4_e2m1fn_x2)
+        pad = lambda rows: (rows + 127) // 128 * 128 * ((K // 16 + 3) // 4 * 4)
+        sa = torch.full((pad(M),), 0.5, device=device).to(torch.float8_e4m3fn)
+        sb = torch.full((pad(N),), 0.5, device=device).to(torch.float8_e4m3fn)
+        run = lambda: torch._scaled_mm(a, b.t(), sa, sb, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            run()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(20):
+            run()
+        stop.record()
+        torch.cuda.synchronize(device)
+        return 2.0 * M * N * K / (start.elapsed_time(stop) / 20 * 1e-3) / 1e12
+    except Exception:  # noqa: BLE001 - optional reference, any failure just omits it
+        return None
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -426,19 +451,28 @@ def run_ours(args) -> None:
         # measured on this pool; the nominal dense FP4 figure is 9000 TFLOP/s).
         peak_tf = 4.0 * bf16_peak if fp4 else bf16_peak
         achieved = flops_per_rank / gemm_s / 1e12
+        gemm_kernel = ("gemm_fp4_pair_kernel" if os.environ.get("UE5M3_FP4_CTA_PAIR", "1") != "0" else "gemm_fp4_kernel") \
+            if fp4 else "gemm_issue_rz_kernel"
+        library_tf = _library_fp4_reference(torch, device) if fp4 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None,
             "dtype": ("fp4 (e2m1 x ue5m3->ue4m3 block scales) tensor-core MMA, fp32 accumulate" if fp4
                       else "fp4(e2m1)xue5m3 codes as encoded bf16 -> fp32 RZ accumulate"),
-            "data": "synthetic", "config": {**_config(world), "gemm_kernel": "gemm_fp4_kernel" if fp4 else "gemm_issue_rz_kernel"},
+            "data": "synthetic", "config": {**_config(world), "gemm_kernel": gemm_kernel},
             "roofline": {
-                "kernel": "gemm_fp4_kernel" if fp4 else "gemm_issue_rz_kernel", "bound": "tensor",
-                "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": None,
+                "kernel": gemm_kernel, "bound": "tensor",
+                "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                # DRAM bytes per launch: ncu capture of the M4096 N8192 case (reads 1.03 x the operand
+                # bytes) scaled by the operand bytes of this shape, plus the bf16 output once
+                "traffic": (1.03 * (M * K / 2 + N * K / 2 + (M + N) * K / 16) + M * N * 2) if fp4 else None,
                 "peak_source": (f"4 x {peaks['source']} cuBLAS bf16 sustained ({bf16_peak}); nominal dense FP4 9000"
                                 if fp4 else f"{peaks['source']} cuBLAS bf16 sustained (burst {peaks['bf16_tflops']})"),
                 "frac_of_nominal_fp4_9000": achieved / 9000.0,
+                "library_reference": (None if library_tf is None else {
+                    "what": "cuBLASLt NVFP4 GEMM via torch._scaled_mm, same shape, random codes, 20 launches",
+                    "tflops": library_tf, "frac": achieved / library_tf}),
                 "algorithmic_flops_per_launch": flops_per_rank, "gemm_ms": gemm_s * 1e3,
             },
             "quantize": quant,

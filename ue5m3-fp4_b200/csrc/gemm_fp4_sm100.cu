@@ -221,7 +221,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // fall through to the common exit
     } else if (warp == 0) {
         // ---------------- producer: operands by TMA, scale atoms by bulk copy ----------------
-        if (lane == 0) {
+        {
             uint32_t g = 0;  // stage counter across tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -234,6 +234,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t use = g / kFStages;
                     if (use > 0) {
                         ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 1, j);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
                         if (!ok) break;
                     }
                     unsigned char* sa = smem + s * kFStageBytes;
@@ -243,23 +244,26 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
                     const uint32_t sf_bytes = (uint32_t)issues_here * kSfAtomBytes;
                     const uint32_t tx = kFBytesA + kFBytesB + sf_bytes * (second_b_tile ? 3u : 2u);
-                    mbar_arrive_expect_tx(&bars->full[s], tx);
-                    tma_load_2d(sa, &map_a, &bars->full[s], j * (kFKStage / 2), m0);
-                    tma_load_2d(sb, &map_b, &bars->full[s], j * (kFKStage / 2), n0);
-                    bulk_load(ssfa, p.sfa + ((size_t)tile_m * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
-                              &bars->full[s]);
-                    bulk_load(ssfb, p.sfb + ((size_t)(2 * tile_n) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
-                              &bars->full[s]);
-                    if (second_b_tile)
-                        bulk_load(ssfb + 4 * kSfAtomBytes,
-                                  p.sfb + ((size_t)(2 * tile_n + 1) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&bars->full[s], tx);
+                        tma_load_2d(sa, &map_a, &bars->full[s], j * (kFKStage / 2), m0);
+                        tma_load_2d(sb, &map_b, &bars->full[s], j * (kFKStage / 2), n0);
+                        bulk_load(ssfa, p.sfa + ((size_t)tile_m * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
                                   &bars->full[s]);
+                        bulk_load(ssfb, p.sfb + ((size_t)(2 * tile_n) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                                  &bars->full[s]);
+                        if (second_b_tile)
+                            bulk_load(ssfb + 4 * kSfAtomBytes,
+                                      p.sfb + ((size_t)(2 * tile_n + 1) * sf_k + 4 * j) * kSfAtomBytes, sf_bytes,
+                                      &bars->full[s]);
+                    }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == 1) {
-        // ---------------- scale copies + MMA issue ----------------
-        if (lane == 0) {
+        // ---------------- MMA issue ----------------
+        {
             constexpr uint32_t idesc = make_idesc_fp4(kFM, kFN);
             uint32_t g = 0;
             bool ok = true;
@@ -267,6 +271,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
                 if (it > 0) {  // the previous tile must have left the accumulator
                     ok = mbar_wait(&bars->tmem_empty, (it - 1) & 1, &bars->abort_flag, p.status, 2, it);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                 }
@@ -274,6 +279,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int s = g % kFStages;
                     // scales of this stage are in TMEM, which also means its operands have landed
                     ok = mbar_wait(&bars->sf_full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(smem + s * kFStageBytes);
@@ -281,44 +287,52 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint64_t desc_a = smem_desc_sw128(sa);
                     const uint64_t desc_b = smem_desc_sw128(sb);
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    for (int k = 0; k < issues_here; ++k) {
-                        const uint32_t slot = (uint32_t)(s * 4 + k);
-                        // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
-                        umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                                 (j > 0 || k > 0) ? 1u : 0u, tmem_base + kTmemSfa + slot * 4,
-                                 tmem_base + kTmemSfb + slot * 8);
+                    if (elect_one()) {
+                        for (int k = 0; k < issues_here; ++k) {
+                            const uint32_t slot = (uint32_t)(s * 4 + k);
+                            // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                            umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                     (j > 0 || k > 0) ? 1u : 0u, tmem_base + kTmemSfa + slot * 4,
+                                     tmem_base + kTmemSfb + slot * 8);
+                        }
+                        umma_commit(&bars->empty[s]);
                     }
-                    umma_commit(&bars->empty[s]);
+                    __syncwarp();
                 }
-                if (ok) umma_commit(&bars->tmem_full);
+                if (ok && elect_one()) umma_commit(&bars->tmem_full);
+                __syncwarp();
             }
         }
     } else if (warp >= kFScaleWarp0) {
         // ---------------- scale atoms: shared memory -> TMEM, one slot ring entry per stage ----------------
         // A landed stage (full) implies the MMAs that last read this stage's TMEM scale slots
         // have completed, because the producer refilled the stage only after their commit.
-        if (lane == 0) {
+        {
             uint32_t g = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 for (int j = 0; j < num_stages; ++j, ++g) {
                     const int s = g % kFStages;
                     ok = mbar_wait(&bars->full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 5, j);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t ssfa = smem_u32(smem + s * kFStageBytes) + kFBytesA + kFBytesB;
                     const uint32_t ssfb = ssfa + kFBytesSfa;
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
                     // the issuing thread is the bottleneck of these copies: split them over the warps
-                    for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
-                        const uint32_t slot = (uint32_t)(s * 4 + k);
-                        const uint32_t t_sfa = tmem_base + kTmemSfa + slot * 4;
-                        const uint32_t t_sfb = tmem_base + kTmemSfb + slot * 8;
-                        tmem_copy_sf(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
-                        tmem_copy_sf(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
-                        tmem_copy_sf(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                    if (elect_one()) {
+                        for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
+                            const uint32_t slot = (uint32_t)(s * 4 + k);
+                            const uint32_t t_sfa = tmem_base + kTmemSfa + slot * 4;
+                            const uint32_t t_sfb = tmem_base + kTmemSfb + slot * 8;
+                            tmem_copy_sf(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
+                            tmem_copy_sf(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
+                            tmem_copy_sf(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                        }
+                        umma_commit(&bars->sf_full[s]);
                     }
-                    umma_commit(&bars->sf_full[s]);
+                    __syncwarp();
                 }
             }
         }
@@ -457,7 +471,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // fall through to the common exit
     } else if (warp == 0) {
         // ---------------- producer (both CTAs): own A rows, own B half, own scale atoms ----------------
-        if (lane == 0) {
+        {
             uint32_t g = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
@@ -473,27 +487,31 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     if (use > 0) {
                         ok = mbar_wait_cluster(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status,
                                                where_base + 1, j);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
                         if (!ok) break;
                     }
                     unsigned char* sa = smem + s * kPStageBytes;
                     unsigned char* sb = sa + kPBytesA;
                     unsigned char* ssfa = sb + kPBytesB;
                     unsigned char* ssfb = ssfa + kFBytesSfa;
-                    // out-of-range rows / atoms are zero-filled and still counted, so the byte
-                    // count of a stage is constant
-                    if (leader) mbar_arrive_expect_tx(&bars->full[s], 2 * kPStageBytes);
                     const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[s]), 0);
-                    tma_load_2d_pair(sa, &map_a, full_leader, j * (kFKStage / 2), m0);
-                    tma_load_2d_pair(sb, &map_b, full_leader, j * (kFKStage / 2), n0);
-                    tma_load_2d_pair(ssfa, &map_sfa, full_leader, 0, sfa_row + 4 * j);
-                    tma_load_2d_pair(ssfb, &map_sfb, full_leader, 0, sfb_row + 4 * j);
-                    tma_load_2d_pair(ssfb + 4 * kSfAtomBytes, &map_sfb, full_leader, 0, sfb_row + sf_k + 4 * j);
+                    if (elect_one()) {
+                        // out-of-range rows / atoms are zero-filled and still counted, so the byte
+                        // count of a stage is constant
+                        if (leader) mbar_arrive_expect_tx(&bars->full[s], 2 * kPStageBytes);
+                        tma_load_2d_pair(sa, &map_a, full_leader, j * (kFKStage / 2), m0);
+                        tma_load_2d_pair(sb, &map_b, full_leader, j * (kFKStage / 2), n0);
+                        tma_load_2d_pair(ssfa, &map_sfa, full_leader, 0, sfa_row + 4 * j);
+                        tma_load_2d_pair(ssfb, &map_sfb, full_leader, 0, sfb_row + 4 * j);
+                        tma_load_2d_pair(ssfb + 4 * kSfAtomBytes, &map_sfb, full_leader, 0, sfb_row + sf_k + 4 * j);
+                    }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issue (leader only) ----------------
-        if (lane == 0 && leader) {
+        if (leader) {
             constexpr uint32_t idesc = make_idesc_fp4(kPM, kFN);
             const uint32_t empty_peer0 = map_to_cta(smem_u32(&bars->empty[0]), 1);
             const uint32_t tmem_full_peer = map_to_cta(smem_u32(&bars->tmem_full), 1);
@@ -504,6 +522,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 if (it > 0) {  // both CTAs must have drained the previous tile
                     ok = mbar_wait_cluster(&bars->tmem_empty, (it - 1) & 1, &bars->abort_flag, p.status,
                                            where_base + 2, it);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                 }
@@ -511,6 +530,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const int s = g % kPStages;
                     ok = mbar_wait(&bars->sf_full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
                                    where_base + 3, j);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(smem + s * kPStageBytes);
@@ -518,25 +538,30 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const uint64_t desc_a = smem_desc_sw128(sa);
                     const uint64_t desc_b = smem_desc_sw128(sb);
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    for (int k = 0; k < issues_here; ++k) {
-                        const uint32_t slot = (uint32_t)(s * 4 + k);
-                        umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                                      (j > 0 || k > 0) ? 1u : 0u, tmem_base + kPTmemSfa + slot * 4,
-                                      tmem_base + kPTmemSfb + slot * 8);
+                    if (elect_one()) {
+                        for (int k = 0; k < issues_here; ++k) {
+                            const uint32_t slot = (uint32_t)(s * 4 + k);
+                            umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                          (j > 0 || k > 0) ? 1u : 0u, tmem_base + kPTmemSfa + slot * 4,
+                                          tmem_base + kPTmemSfb + slot * 8);
+                        }
+                        // the stage is free in both CTAs once these MMAs have completed (a relay of
+                        // the leader's barrier through its producer was measured: far slower)
+                        umma_commit_pair(smem_u32(&bars->empty[s]));
+                        umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
                     }
-                    // the stage is free in both CTAs once these MMAs have completed
-                    umma_commit_pair(smem_u32(&bars->empty[s]));
-                    umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
+                    __syncwarp();
                 }
-                if (ok) {
+                if (ok && elect_one()) {
                     umma_commit_pair(smem_u32(&bars->tmem_full));
                     umma_commit_pair(tmem_full_peer);
                 }
+                __syncwarp();
             }
         }
     } else if (warp >= kFScaleWarp0) {
         // ---------------- scale atoms shared -> TMEM in both CTAs (issued by the leader) ----------------
-        if (lane == 0 && leader) {
+        if (leader) {
             uint32_t g = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
@@ -544,20 +569,24 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const int s = g % kPStages;
                     ok = mbar_wait_cluster(&bars->full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
                                            where_base + 5, j);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t ssfa = smem_u32(smem + s * kPStageBytes) + kPBytesA + kPBytesB;
                     const uint32_t ssfb = ssfa + kFBytesSfa;
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
-                        const uint32_t slot = (uint32_t)(s * 4 + k);
-                        const uint32_t t_sfa = tmem_base + kPTmemSfa + slot * 4;
-                        const uint32_t t_sfb = tmem_base + kPTmemSfb + slot * 8;
-                        tmem_copy_sf_pair(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
-                        tmem_copy_sf_pair(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
-                        tmem_copy_sf_pair(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                    if (elect_one()) {
+                        for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
+                            const uint32_t slot = (uint32_t)(s * 4 + k);
+                            const uint32_t t_sfa = tmem_base + kPTmemSfa + slot * 4;
+                            const uint32_t t_sfb = tmem_base + kPTmemSfb + slot * 8;
+                            tmem_copy_sf_pair(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
+                            tmem_copy_sf_pair(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
+                            tmem_copy_sf_pair(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                        }
+                        umma_commit_pair(smem_u32(&bars->sf_full[s]));
                     }
-                    umma_commit_pair(smem_u32(&bars->sf_full[s]));
+                    __syncwarp();
                 }
             }
         }
@@ -700,13 +729,13 @@ static int make_sf_map(CUtensorMap* map, const void* base, int64_t atoms) {
     return UE5M3_OK;
 }
 
-// The CTA-pair kernel is selected by UE5M3_FP4_CTA_PAIR=1 in the environment (read at every
-// call).  It is bit-equal to the single-CTA kernel and moves a third less data per SM, but on
-// the benchmark shape it is the slower of the two (0.39 ms against 0.37 ms): both are bound by
-// the issue rate of the tcgen05 instruction stream, not by data movement.
-static bool use_cta_pair() {
+// The CTA-pair kernel is used when there is more than one 128-row tile; UE5M3_FP4_CTA_PAIR=0/1
+// in the environment (read at every call) forces the single-CTA / the pair kernel.  The two are
+// bit-equal; on the benchmark shape the pair kernel takes 0.337 ms against 0.353 ms.
+static bool use_cta_pair(int64_t M) {
     const char* e = getenv("UE5M3_FP4_CTA_PAIR");
-    return e && e[0] == '1';
+    if (e && (e[0] == '0' || e[0] == '1')) return e[0] == '1';
+    return M > 128;
 }
 
 }  // namespace ue5m3
@@ -750,7 +779,7 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
         return UE5M3_ERR_ALIGNMENT;
     if (((K / 2) % 16) != 0) return UE5M3_ERR_ALIGNMENT;  // TMA row pitch
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
-    const bool pair = use_cta_pair();
+    const bool pair = use_cta_pair(M);
     const int64_t tile_rows = pair ? kPM : kFM;
     const int64_t tiles_m = (M + tile_rows - 1) / tile_rows, tiles_n = (N + kFN - 1) / kFN;
     if (tiles_m * tiles_n > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;

@@ -47,6 +47,21 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
     return done != 0;
 }
 
+// One lane of a converged warp.  Roles that issue TMA / tcgen05 instructions keep their
+// control flow warp-uniform and predicate only the issue on this, so that addresses and
+// descriptors stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xFFFFFFFF;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // Bounded wait.  Returns false when the clock budget expired or another role raised the
 // CTA's abort flag; on expiry records (site, iteration, block) in the caller's status words.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, int* abort_flag,
