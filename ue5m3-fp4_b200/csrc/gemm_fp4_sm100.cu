@@ -378,8 +378,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // tile, so a K=256 stage moves 38 KiB per CTA instead of 54 KiB and every MMA reads 8 KiB of
 // shared memory per CTA instead of 12 KiB.  The leader CTA (rank 0) issues the scale copies,
 // the MMAs and the commits for both; every load of both CTAs reports to the leader's `full`
-// barrier (plain TMA loads with cta_group::2, no multicast).  Each CTA drains its own 128
-// accumulator rows.
+// barrier (plain per-CTA TMA loads with cta_group::2, each CTA fetching only its own data).
+// Each CTA drains its own 128 accumulator rows.
 // ---------------------------------------------------------------------------------------
 constexpr int kPM = 256;
 constexpr int kPStages = 5;

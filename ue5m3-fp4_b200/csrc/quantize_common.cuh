@@ -133,6 +133,50 @@ __device__ __forceinline__ void load_unit<float>(const float* x, int64_t unit, f
     for (int i = 0; i < 8; ++i) v[8 + i] = __uint_as_float(w[i]);
 }
 
+// A 16-element unit as it sits in memory (bf16: 8 words, fp32: 16 words); kept raw until the
+// unit is processed so that only one unit's fp32 values are live at a time.
+template <typename T>
+struct RawUnit {
+    uint32_t w[sizeof(T) * 4];
+};
+
+template <typename T>
+__device__ __forceinline__ void load_raw_unit(const T* x, int64_t unit, RawUnit<T>& r);
+
+template <>
+__device__ __forceinline__ void load_raw_unit<__nv_bfloat16>(const __nv_bfloat16* x, int64_t unit,
+                                                             RawUnit<__nv_bfloat16>& r) {
+    ldg256(x + unit * 16, r.w);
+}
+
+template <>
+__device__ __forceinline__ void load_raw_unit<float>(const float* x, int64_t unit, RawUnit<float>& r) {
+    uint32_t a[8], b[8];
+    ldg256(x + unit * 16, a);
+    ldg256(x + unit * 16 + 8, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { r.w[i] = a[i]; r.w[8 + i] = b[i]; }
+}
+
+__device__ __forceinline__ void unit_values(const RawUnit<__nv_bfloat16>& r, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(r.w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(r.w[i] & 0xFFFF0000u);
+    }
+}
+
+__device__ __forceinline__ void unit_values(const RawUnit<float>& r, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r.w[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ void zero_raw_unit(RawUnit<T>& r) {
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(T) * 4); ++i) r.w[i] = 0u;
+}
+
 // 16 random bytes of one unit, packed four per word
 template <int BITS>
 __device__ __forceinline__ void load_unit_bits(const void* bits, int64_t unit, uint32_t (&r)[4]) {

@@ -48,19 +48,18 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
         const bool valid = row < a.rows;
         const int64_t unit0 = (row * a.cols + ka * 64) / 16;  // first 16-element unit of this lane
 
-        float v[4][16];
+        RawUnit<T> raw[4];
         uint32_t rb[4][4];
         if (valid) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                load_unit<T>(x, unit0 + u, v[u]);
+                load_raw_unit<T>(x, unit0 + u, raw[u]);
                 if (kSr) load_unit_bits<BITS>(a.bits, unit0 + u, rb[u]);
             }
         } else {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[u][i] = 0.0f;
+                zero_raw_unit<T>(raw[u]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) rb[u][i] = 0u;
             }
@@ -69,9 +68,11 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
         float m[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
+            float v[16];
+            unit_values(raw[u], v);
             m[u] = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) m[u] = fmaxf(m[u], fabsf(v[u][i]));
+            for (int i = 0; i < 16; ++i) m[u] = fmaxf(m[u], fabsf(v[i]));
         }
         if (B == 32) {
             m[0] = m[1] = fmaxf(m[0], m[1]);
@@ -105,14 +106,16 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
             sf_word |= (uint32_t)code4 << (8 * u);
             const float scale = ue5m3_decode(code[u]);
             const float rcp = payload_multiplier(scale, ts);
+            float v[16];
+            unit_values(raw[u], v);
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) mul2_rn(v[u][i], v[u][i + 1], rcp);
+            for (int i = 0; i < 16; i += 2) mul2_rn(v[i], v[i + 1], rcp);
             if (RMODE == kRoundTteHw) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float w[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) w[i] = v[u][h * 8 + i];
+                    for (int i = 0; i < 8; ++i) w[i] = v[h * 8 + i];
                     packed[u][h] = e2m1_pack8_hw(w);
                 }
             } else if (kSr) {
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                 for (int h = 0; h < 2; ++h) {
                     float w[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) w[i] = v[u][h * 8 + i];
+                    for (int i = 0; i < 8; ++i) w[i] = v[h * 8 + i];
                     packed[u][h] = e2m1_pack8_sr(w, rb[u][2 * h], rb[u][2 * h + 1]);
                 }
             } else {
@@ -129,7 +132,7 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                     packed[u][h] = 0u;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        packed[u][h] += e2m1_nibble<false>(v[u][h * 8 + i], 0u) * (1u << (4 * i));
+                        packed[u][h] += e2m1_nibble<false>(v[h * 8 + i], 0u) * (1u << (4 * i));
                 }
             }
         }

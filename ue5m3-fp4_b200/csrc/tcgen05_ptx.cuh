@@ -243,7 +243,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 // 2-D tiled TMA load into this CTA's shared memory whose completion is counted on an mbarrier
-// given by shared::cluster address (the pair leader's); no multicast.
+// given by shared::cluster address (the pair leader's); the data goes to this CTA only.
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
                                                  int x, int y) {
     asm volatile(
