@@ -185,6 +185,17 @@ int ue5m3_quantize_fp4_operand(const void *x, int dtype, int64_t rows, int64_t c
                                uint8_t *sf, uint8_t *scales, int *window_flag, void *stream);
 
 /*
+ * The same for an operand that is x transposed: the reduction axis is the ROW axis of x
+ * (blocking UE5M3_BLOCK_COL: block x 1 blocks, or UE5M3_BLOCK_2D), rows = K, K % 64 == 0.
+ * Writes codes_t [cols, K/2] and the scale atoms of the cols x K operand (dgrad W^T, wgrad dY^T
+ * and X^T of nn/linear.py:359-363,385 without the transposed fp32 copies).
+ */
+int ue5m3_quantize_fp4_operand_t(const void *x, int dtype, int64_t rows, int64_t cols, int block,
+                                 int blocking, const float *amax_dev, float target, int rounding,
+                                 const void *bits, int bits_dtype, int shift, uint8_t *codes_t,
+                                 uint8_t *sf_t, int *window_flag, void *stream);
+
+/*
  * Probe-matched GEMM on PACKED operands with the FP4 block-scaled tensor cores:
  *   out[M,N] = epilogue( 2^shift_sum * sum over K=64 issues of (A codes x scales) . (B codes x scales) )
  * a_codes [M, K/2], b_codes [N, K/2] (E2M1 nibbles, reduction axis contiguous); a_sf, b_sf from

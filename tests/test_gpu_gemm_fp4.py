@@ -233,3 +233,40 @@ def test_cta_pair_kernel_is_bit_equal_to_the_single_cta_kernel_and_the_oracle(b2
     single, _ = _case(b200, a, bt, block=block, two_d=two_d)
     assert np.array_equal(pair, single)
     assert np.array_equal(pair, expect)
+
+
+@pytest.mark.parametrize("k,rows,block,blocking,sr,dtype", [
+    (128, 64, 16, "col", False, torch.bfloat16),
+    (320, 200, 16, "col", True, torch.bfloat16),
+    (256, 77, 32, "col", False, torch.float32),
+    (192, 160, 16, "2d", False, torch.bfloat16),
+    (448, 300, 16, "2d", False, torch.float32),
+    (128, 96, 32, "2d", False, torch.bfloat16),
+    (1024, 1000, 32, "col", True, torch.bfloat16),
+])
+def test_one_pass_transposed_operand_equals_quantize_then_pack(b200, k, rows, block, blocking, sr, dtype):
+    """ue5m3_quantize_fp4_operand_t (operand = x^T: codes_t + UE4M3 atoms in one launch) against
+    ue5m3_quantize with transposed outputs followed by ue5m3_pack_scales_ue4m3."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(rows * 5 + k)
+    x = torch.randn(k, rows, generator=g)  # x is [K, rows]: the operand is its transpose
+    x = x.to(torch.bfloat16).float() if dtype is torch.bfloat16 else x
+    bits = random_bits((k, rows), rows + k, torch.uint8) if sr else None
+    amax = torch.tensor([float(x.abs().max())], device=dev)
+    code = b200.BLOCK_COL if blocking == "col" else b200.BLOCK_2D
+    rounding = "StochasticFast" if sr else "TTE"
+    xd = x.to(dtype).cuda()
+    bd = None if bits is None else bits.cuda()
+    b200.window_flag(dev).zero_()
+    shift = b200.scale_shift_for_target(448.0)
+    op = b200.quantize_fp4_operand(xd, block_size=block, blocking=code, transposed=True, tensor_amax=amax,
+                                   scale_target=448.0, rounding=rounding, random_bits=bd)
+    two = b200.quantize_packed(xd, block_size=block, blocking=code, tensor_amax=amax, scale_target=448.0,
+                               rounding=rounding, random_bits=bd, packed=False, packed_t=True)
+    sf = b200.pack_scales(two.scales_t, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d",
+                          shift=shift)
+    assert int(b200.window_flag(dev).item()) == 0
+    assert (op.rows, op.k) == (rows, k)
+    assert torch.equal(op.codes, two.codes_t)
+    assert torch.equal(op.scale_factors, sf)

@@ -61,8 +61,9 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
 #pragma unroll
             for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[k][i]));
             if (kLanesPerBlock == 2) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
-            const uint32_t code = block_scale_code(m, ts);
-            const float scale = ue5m3_decode(code);
+            uint32_t code;
+            float scale;
+            block_scale_converged(m, ts, code, scale);
             const float rcp = payload_multiplier(scale, ts);
 #pragma unroll
             for (int i = 0; i < 16; i += 2) mul2_rn(v[k][i], v[k][i + 1], rcp);
@@ -179,6 +180,7 @@ struct TileSmem {
     __align__(16) uint8_t stage_t[kTileCols][kStageTPitch];   // codes_t: [col][row/2]
     __align__(16) uint8_t stage_n[kTileRows][kTileCols / 2];  // codes  : [row][col/2]
     __align__(8) uint8_t scale_t[kTileCols][8];               // COL scales_t: [col][row group]
+    __align__(8) uint8_t sf_t[kTileCols][8];                  // UE4M3 bytes per 16 rows of the tile
 };
 
 struct TileArgs {
@@ -196,6 +198,10 @@ struct TileArgs {
     int fake_dtype;
     int fake_domain;
     int vec_ok;  // x (and bits) rows start on 16-byte boundaries
+    // transposed operand of the FP4 GEMM: scale atoms [ceil(cols/128)][rows/64][128 words]
+    uint32_t* sf_t;
+    int shift;
+    int* window_flag;
 };
 
 template <typename T, int B, bool TWO_D, int RMODE, int BITS>
@@ -257,6 +263,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
     const int64_t nbr = (a.rows + B - 1) / B;  // scale rows
     const int64_t nbc = (a.cols + B - 1) / B;  // scale columns (2D)
     const bool want_fake = a.fake != nullptr || a.fake_t != nullptr;
+    bool bad = false;
 #pragma unroll 1
     for (int item = tid; item < kItems; item += 256) {
         const int c = item % kTileCols;
@@ -276,6 +283,15 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
         const float scale = ue5m3_decode(code);
         const float rcp = payload_multiplier(scale, ts);
         const float sd = __fmul_rn(scale, ts.dec);
+        if (a.sf_t) {
+            int code4 = (int)code - ((8 + a.shift) << 3);
+            if (code4 < 8 || code4 > 0x7E) {
+                if (c0 + c < a.cols && r0 + (int64_t)g * B < a.rows) bad = true;
+                code4 = code4 < 8 ? 8 : 0x7E;
+            }
+#pragma unroll
+            for (int h = 0; h < B / 16; ++h) s.sf_t[c][g * (B / 16) + h] = (uint8_t)code4;
+        }
         uint32_t nib[B];
         if (RMODE == kRoundTteHw) {
 #pragma unroll
@@ -365,6 +381,26 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
             int c = i / kGroups, g = i % kGroups;
             int64_t sr = r0 / B + g;
             if (c0 + c < a.cols && sr < nbr) a.scales_t[(c0 + c) * nbr + sr] = s.scale_t[c][g];
+        }
+    }
+    if (a.sf_t) {
+        // 64 operand rows (tile columns) x two K atoms (tile rows 0..63, 64..127): one word each
+        if (bad) atomicExch(a.window_flag, 1);
+        const int64_t k_atoms = a.rows / 64;
+        if (tid < 2 * kTileCols) {
+            const int c = tid >> 1, half = tid & 1;
+            const int64_t orow = c0 + c;
+            const int64_t ka = r0 / 64 + half;
+            if (ka < k_atoms) {
+                uint32_t word = *reinterpret_cast<const uint32_t*>(&s.sf_t[c][4 * half]);
+                if (orow >= a.cols) word = 0x38383838u;
+                a.sf_t[((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)] = word;
+                // the last column tile also pads the rest of its 128-row atom
+                if (c0 + kTileCols >= a.cols && ((c0 + kTileCols) & 127) != 0) {
+                    const int64_t prow = orow + kTileCols;
+                    a.sf_t[((prow >> 7) * k_atoms + ka) * 128 + (prow & 31) * 4 + ((prow >> 5) & 3)] = 0x38383838u;
+                }
+            }
         }
     }
     if (a.fake) {
@@ -536,11 +572,12 @@ static int dispatch_tile(int rmode, int bits_dtype, const TileArgs& args, cudaSt
 
 using namespace ue5m3;
 
-extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int block,
-                              int blocking, const float* amax_dev, float target, int rounding,
-                              const void* bits, int bits_dtype, uint8_t* codes, uint8_t* scales,
-                              uint8_t* codes_t, uint8_t* scales_t, void* fake, void* fake_t,
-                              int fake_dtype, int fake_domain, void* stream_v) {
+static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t cols, int block,
+                             int blocking, const float* amax_dev, float target, int rounding,
+                             const void* bits, int bits_dtype, uint8_t* codes, uint8_t* scales,
+                             uint8_t* codes_t, uint8_t* scales_t, void* fake, void* fake_t,
+                             int fake_dtype, int fake_domain, uint32_t* sf_t, int shift,
+                             int* window_flag, void* stream_v) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (!x || !amax_dev || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
@@ -600,6 +637,7 @@ extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t co
     args.bits = bits; args.codes = codes; args.scales = scales; args.codes_t = codes_t;
     args.scales_t = scales_t; args.fake = fake; args.fake_t = fake_t; args.fake_dtype = fake_dtype;
     args.fake_domain = fake_domain;
+    args.sf_t = sf_t; args.shift = shift; args.window_flag = window_flag;
     const bool fake_vec = !fake || (((uintptr_t)fake % 16) == 0 && (cols * fsize) % 16 == 0);
     const bool fake_t_ok = !fake_t || ((uintptr_t)fake_t % 16) == 0;
     if (!fake_t_ok) return UE5M3_ERR_ALIGNMENT;
@@ -615,6 +653,31 @@ extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t co
 #undef UE5M3_DT
     if (status != UE5M3_OK) return status;
     return check_launch();
+}
+
+extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int block,
+                              int blocking, const float* amax_dev, float target, int rounding,
+                              const void* bits, int bits_dtype, uint8_t* codes, uint8_t* scales,
+                              uint8_t* codes_t, uint8_t* scales_t, void* fake, void* fake_t,
+                              int fake_dtype, int fake_domain, void* stream_v) {
+    return quantize_dispatch(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
+                             bits_dtype, codes, scales, codes_t, scales_t, fake, fake_t, fake_dtype,
+                             fake_domain, nullptr, 0, nullptr, stream_v);
+}
+
+extern "C" int ue5m3_quantize_fp4_operand_t(const void* x, int dtype, int64_t rows, int64_t cols,
+                                            int block, int blocking, const float* amax_dev,
+                                            float target, int rounding, const void* bits,
+                                            int bits_dtype, int shift, uint8_t* codes_t, uint8_t* sf_t,
+                                            int* window_flag, void* stream_v) {
+    if (!codes_t || !sf_t || !window_flag || shift < -8 || shift > 16) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (blocking != UE5M3_BLOCK_COL && blocking != UE5M3_BLOCK_2D) return UE5M3_ERR_UNSUPPORTED;
+    if (rows % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if ((uintptr_t)sf_t % 16) return UE5M3_ERR_ALIGNMENT;
+    return quantize_dispatch(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
+                             bits_dtype, nullptr, nullptr, codes_t, nullptr, nullptr, nullptr,
+                             UE5M3_DTYPE_BF16, UE5M3_FAKE_NONE, reinterpret_cast<uint32_t*>(sf_t), shift,
+                             window_flag, stream_v);
 }
 
 extern "C" int ue5m3_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t rows,

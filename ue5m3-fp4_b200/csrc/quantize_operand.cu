@@ -91,12 +91,13 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
         uint32_t code[4];
         uint32_t sf_word = 0u;
         uint32_t packed[4][2];
+        float scale = 1.0f;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (B == 32 && (u & 1)) {
-                code[u] = code[u - 1];
+                code[u] = code[u - 1];  // same 32-wide block as the previous unit: same scale
             } else {
-                code[u] = block_scale_code(m[u], ts);
+                block_scale_converged(m[u], ts, code[u], scale);
             }
             int code4 = (int)code[u] - rebias;
             if (code4 < 8 || code4 > 0x7E) {
@@ -104,7 +105,6 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                 code4 = code4 < 8 ? 8 : 0x7E;
             }
             sf_word |= (uint32_t)code4 << (8 * u);
-            const float scale = ue5m3_decode(code[u]);
             const float rcp = payload_multiplier(scale, ts);
             float v[16];
             unit_values(raw[u], v);

@@ -62,6 +62,26 @@ __device__ __forceinline__ uint32_t block_scale_code(float block_amax, const Ten
     return code == 0u ? 0x78u : code;  // 0x78 = 1.0
 }
 
+// block_scale_code + ue5m3_decode for a CONVERGED warp: the normal range (ideal >= 2^-14) is
+// four integer operations whose rounded bits are the decoded scale itself; the subnormal range
+// (including the all-zero block -> 1.0 rule) is taken as a warp-uniform branch only when some
+// lane needs it.
+__device__ __forceinline__ void block_scale_converged(float block_amax, const TensorScale& t,
+                                                      uint32_t& code, float& scale) {
+    float ideal = fminf(__fmul_rn(block_amax, t.mult), kScaleMax);
+    if (block_amax == 0.0f) ideal = 0.0f;
+    const uint32_t b = __float_as_uint(ideal);
+    const uint32_t r = (b + 0x7FFFFu + ((b >> 20) & 1u)) & 0xFFF00000u;  // RNE to three fraction bits
+    code = (r >> 20) - (112u << 3);
+    scale = __uint_as_float(r);
+    if (__any_sync(0xFFFFFFFFu, ideal < 6.103515625e-05f)) {
+        if (ideal < 6.103515625e-05f) {
+            code = block_scale_code(block_amax, t);
+            scale = ue5m3_decode(code);
+        }
+    }
+}
+
 // Reciprocal-then-multiply payload multiplier (formats.py:439-443).
 __device__ __forceinline__ float payload_multiplier(float scale, const TensorScale& t) {
     return __frcp_rn(__fmul_rn(scale, t.dec));  // correctly rounded, same bits as 1/d
@@ -154,14 +174,11 @@ __device__ __forceinline__ void e2m1_unpack2_hw(uint32_t byte, float& lo, float&
 // ---- stochastic rounding of eight values at once -----------------------------------
 // Same rule as e2m1_index_sr, arranged so that the integer pipe does as little as possible
 // and nothing is selected per element.  With a = min(|u|, 6) two candidate indices are built:
-//  * H, exact for a >= 1: one byte permute builds (4 << 24) | (r << 16) | 0x8000
-//    = ((2r+1) << 15) + (4 << 24) from the packed random bytes; the TOP BYTE of
-//    4*bits(a) + that word is the index (2..7, nothing else set).
-//  * L = floor(fl(2a + mid)), exact for a < 2 (for a in [1, 2) the sum is exact and equals the
-//    carry rule; for a >= 2 it is >= 4).  mid = (2r+1) * 2^-9 comes from a second permute that
-//    builds the float 2^23 + r and one exact fma: (2^23 + r) * 2^-8 - (2^15 - 2^-9).  These
-//    run as packed fp32 instructions, two elements each; floor() is the low byte of
-//    RZ(z + 2^23).
+//  * H, exact for a >= 1: the TOP BYTE of 4*bits(a) + ((2r+1) << 15) + (4 << 24) is the
+//    index (2..7, nothing else set).
+//  * L = floor(fl(2a + mid)), mid = (2r+1) * 2^-9, exact for a < 2 (for a in [1, 2) the sum is
+//    exact and equals the carry rule; for a >= 2 it is >= 4).  Packed fp32 instructions, two
+//    elements each; floor() is the low byte of RZ(z + 2^23).
 // Four H bytes and four L bytes are gathered into words and the index is, per byte,
 // L >= 4 ? H : L.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
@@ -172,15 +189,19 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t select
     return d;
 }
 
-// t (top byte = H) and s (low byte = L, upper bytes 0x4B0000) of two elements
+// t (top byte = H) and s (low byte = L, upper bytes 0x4B0000) of two elements.  One permute
+// per element builds the word 0x4B00rr80, which serves twice: as a float it is
+// 2^23 + 128*(2r+1), so mid = word * 2^-16 - 128 in one exact fma; as an integer its multiple
+// by 256 is (2r+1) << 15 (the 0x4B falls off the top), the random offset of the a >= 1 path.
 __device__ __forceinline__ void e2m1_sr_candidates2(float u0, float u1, uint32_t rword, int k,
                                                     uint32_t& t0, uint32_t& t1, uint32_t& s0,
                                                     uint32_t& s1) {
     const float a0 = fminf(fabsf(u0), 6.0f), a1 = fminf(fabsf(u1), 6.0f);
-    t0 = __float_as_uint(a0) * 4u + __byte_perm(rword, 0x00048000u, 0x6054u | ((uint32_t)k << 8));
-    t1 = __float_as_uint(a1) * 4u + __byte_perm(rword, 0x00048000u, 0x6054u | ((uint32_t)(k + 1) << 8));
-    const uint32_t m0 = __byte_perm(rword, 0x4B000000u, 0x7540u | (uint32_t)k);
-    const uint32_t m1 = __byte_perm(rword, 0x4B000000u, 0x7540u | (uint32_t)(k + 1));
+    // bytes: [0] = 0x80, [1] = r, [2] = 0x00, [3] = 0x4B
+    const uint32_t m0 = __byte_perm(rword, 0x4B000080u, 0x7504u | ((uint32_t)k << 4));
+    const uint32_t m1 = __byte_perm(rword, 0x4B000080u, 0x7504u | ((uint32_t)(k + 1) << 4));
+    t0 = m0 * 256u + (__float_as_uint(a0) * 4u + 0x04000000u);
+    t1 = m1 * 256u + (__float_as_uint(a1) * 4u + 0x04000000u);
     asm("{\n"
         ".reg .b64 m, a, z, c8, cm, c2, cb;\n"
         "mov.b64 m, {%2, %3};\n"
@@ -195,7 +216,7 @@ __device__ __forceinline__ void e2m1_sr_candidates2(float u0, float u1, uint32_t
         "mov.b64 {%0, %1}, z;\n"
         "}\n"
         : "=r"(s0), "=r"(s1)
-        : "r"(m0), "r"(m1), "f"(a0), "f"(a1), "f"(0.00390625f), "f"(-32767.998046875f), "f"(2.0f),
+        : "r"(m0), "r"(m1), "f"(a0), "f"(a1), "f"(1.52587890625e-05f), "f"(-128.0f), "f"(2.0f),
           "f"(8388608.0f));
 }
 

@@ -77,6 +77,8 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_pack_scales_ue4m3.argtypes = [p, i64, i64, i32, i32, i32, p, p, p]
     lib.ue5m3_quantize_fp4_operand.restype = i32
     lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
+    lib.ue5m3_quantize_fp4_operand_t.restype = i32
+    lib.ue5m3_quantize_fp4_operand_t.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
     lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, i32, p, i32, i64, p, p]
     lib.ue5m3_test_e2m1_cvt.restype = i32

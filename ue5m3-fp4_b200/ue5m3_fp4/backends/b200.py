@@ -415,6 +415,10 @@ def quantize_fp4_operand(
             and x.is_contiguous() and x.data_ptr() % 32 == 0:
         return _quantize_fp4_operand_fused(x, block_size, blocking, tensor_amax, scale_target, rounding,
                                            random_bits, shift)
+    if transposed and blocking in (BLOCK_COL, BLOCK_2D) and x.ndim == 2 and x.shape[0] % 64 == 0 \
+            and x.is_contiguous():
+        return _quantize_fp4_operand_fused(x, block_size, blocking, tensor_amax, scale_target, rounding,
+                                           random_bits, shift, transposed=True)
     packed = quantize_packed(
         x, block_size=block_size, blocking=blocking, tensor_amax=tensor_amax, scale_target=scale_target,
         rounding=rounding, random_bits=random_bits, packed=not transposed, packed_t=transposed,
@@ -428,8 +432,9 @@ def quantize_fp4_operand(
 
 def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tensor_amax: Tensor,
                                 scale_target: float, rounding, random_bits: Tensor | None, shift: int,
-                                *, want_scales: bool = False):
-    """One launch: codes and tensor-core scale atoms (ue5m3_quantize_fp4_operand)."""
+                                *, want_scales: bool = False, transposed: bool = False):
+    """One launch: codes and tensor-core scale atoms (ue5m3_quantize_fp4_operand, or
+    ue5m3_quantize_fp4_operand_t for the operand x^T)."""
 
     _require_cuda(x, "x")
     if tensor_amax.device != x.device or tensor_amax.dtype is not torch.float32 or tensor_amax.numel() != 1:
@@ -445,9 +450,23 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
             raise ValueError("random bits must be contiguous, on the operand's device and of its shape")
     elif random_bits is not None:
         raise ValueError("random bits are only valid with stochastic rounding")
-    rows, k = x.shape
     dev = x.device
     lib = _native.load()
+    if transposed:
+        k, rows = x.shape
+        codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
+        sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            status = lib.ue5m3_quantize_fp4_operand_t(
+                x.data_ptr(), _native.dtype_code(x.dtype), k, rows, block_size, blocking,
+                tensor_amax.data_ptr(), float(scale_target),
+                _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
+                _native.ptr(random_bits), _bits_code(random_bits), shift,
+                codes.data_ptr(), sf.data_ptr(), window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+            )
+        _native.check(status, "ue5m3_quantize_fp4_operand_t")
+        return Fp4Operand(codes, sf, shift, rows, k)
+    rows, k = x.shape
     codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
     sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
     scales = None
