@@ -46,6 +46,15 @@ extern "C" {
 #define UE5M3_BITS_NONE 0
 #define UE5M3_BITS_U8 1
 #define UE5M3_BITS_I32 2 /* the reference's dtype, backends/triton/quantization.py:276 */
+/*
+ * No bit tensor: `bits` points to two uint64 on the device, {seed, stream}, and the byte of
+ * element e (row-major index in x) is byte e % 16 of Philox4x32-10 with key = seed and
+ * counter = {e / 16, stream} (words c0..c3 little-endian).  The reference draws its bits
+ * from a torch generator (nn/linear.py:371-384), a stream that no kernel can reproduce;
+ * ue5m3_philox_bytes writes the very bytes this mode uses, so that a run can be replayed
+ * with an explicit UE5M3_BITS_U8 tensor.
+ */
+#define UE5M3_BITS_PHILOX 3
 
 /* block geometry */
 #define UE5M3_BLOCK_ROW 0 /* 1 x B, along the last axis (activations, dY)          */
@@ -168,6 +177,9 @@ int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N
 size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K);
 int ue5m3_pack_scales_ue4m3(const uint8_t *scales, int64_t rows, int64_t K, int block, int two_d,
                             int shift, uint8_t *sf_out, int *window_flag, void *stream);
+
+/* count bytes of the UE5M3_BITS_PHILOX stream {seed, stream} starting at element 0 */
+int ue5m3_philox_bytes(const void *seed_stream_dev, int64_t count, uint8_t *out, void *stream);
 
 /*
  * One-pass quantizer for an operand of ue5m3_gemm_fp4 whose reduction axis is the contiguous

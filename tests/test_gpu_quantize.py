@@ -237,3 +237,92 @@ def test_fake_quantize_gemm_operands_against_oracle(b200, block, two_d, domain):
                          amax=float(b.float().abs().max()), target=448.0, sr=True, bits=bits_b)
     assert np.array_equal(to_np(out_a), qa[domain])
     assert np.array_equal(to_np(out_b), qb[domain])
+
+
+@pytest.mark.parametrize("rows,cols,block,blocking", [(64, 256, 16, "row"), (37, 160, 32, "row"), (128, 192, 16, "col"),
+                                                     (100, 72, 16, "col"), (96, 128, 16, "2d"), (33, 50, 16, "row")])
+def test_counter_based_bits_equal_their_materialised_tensor(b200, rows, cols, block, blocking):
+    """UE5M3_BITS_PHILOX: the quantizer computes its random bytes; the same call with the
+    bytes written out by ue5m3_philox_bytes as an explicit uint8 tensor gives the same bits,
+    on the streaming, the ragged and the tile kernels."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(rows * cols)
+    x = torch.randn(rows, cols, generator=g).to(torch.bfloat16).cuda()
+    amax = torch.tensor([float(x.float().abs().max()) * 0.9], device=dev)
+    stream = b200.PhiloxBits(torch.tensor([0x1234567 + rows, 77 + cols], dtype=torch.int64, device=dev))
+    explicit = stream.materialize((rows, cols))
+    code = {"row": b200.BLOCK_ROW, "col": b200.BLOCK_COL, "2d": b200.BLOCK_2D}[blocking]
+    kw = dict(block_size=block, blocking=code, tensor_amax=amax, rounding="StochasticFast",
+              packed=blocking != "col", packed_t=blocking != "row")
+    a = b200.quantize_packed(x, random_bits=stream, **kw)
+    b = b200.quantize_packed(x, random_bits=explicit, **kw)
+    for name in ("codes", "scales", "codes_t", "scales_t"):
+        ta, tb = getattr(a, name), getattr(b, name)
+        assert (ta is None) == (tb is None)
+        if ta is not None:
+            assert torch.equal(ta, tb), name
+    other = b200.PhiloxBits(torch.tensor([0x1234567 + rows, 78 + cols], dtype=torch.int64, device=dev))
+    assert not torch.equal(other.materialize((rows, cols)), explicit)
+
+
+def test_counter_based_bits_in_the_one_pass_operand_kernels(b200):
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(192, 256, generator=g).to(torch.bfloat16).cuda()
+    amax = torch.tensor([float(x.float().abs().max())], device=dev)
+    stream = b200.PhiloxBits(torch.tensor([99, 3], dtype=torch.int64, device=dev))
+    explicit = stream.materialize(x.shape)
+    for blocking, transposed in [(b200.BLOCK_ROW, False), (b200.BLOCK_COL, True)]:
+        kw = dict(block_size=16, blocking=blocking, transposed=transposed, tensor_amax=amax, scale_target=448.0,
+                  rounding="StochasticFast")
+        a = b200.quantize_fp4_operand(x, random_bits=stream, **kw)
+        b = b200.quantize_fp4_operand(x, random_bits=explicit, **kw)
+        assert torch.equal(a.codes, b.codes) and torch.equal(a.scale_factors, b.scale_factors)
+
+
+def test_counter_based_bits_are_uniform_bytes(b200):
+    dev = torch.device("cuda", 0)
+    stream = b200.PhiloxBits(torch.tensor([42, 7], dtype=torch.int64, device=dev))
+    sample = stream.materialize((1 << 22,)).cpu().numpy()
+    counts = np.bincount(sample, minlength=256)
+    expected = sample.size / 256
+    chi2 = float(((counts - expected) ** 2 / expected).sum())
+    assert 150.0 < chi2 < 400.0, chi2  # 255 degrees of freedom
+    assert abs(float(sample.mean()) - 127.5) < 0.2
+    pairs = np.corrcoef(sample[:-1].astype(np.float64), sample[1:].astype(np.float64))[0, 1]
+    assert abs(pairs) < 0.005
+
+
+def test_philox_known_answer(b200):
+    """Philox4x32-10 with counter 0 and key 0 (the published known-answer vector)."""
+
+    dev = torch.device("cuda", 0)
+    key = torch.tensor([0, 0], dtype=torch.int64, device=dev)
+    raw = b200.PhiloxBits(key).materialize((16,)).cpu().numpy()
+    assert [int(v) for v in raw.view(np.uint32)] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+
+
+def _philox4x32_10(counter, key):
+    """Plain-Python Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3")."""
+
+    c, k = list(counter), list(key)
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * c[0], 0xCD9E8D57 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k[0], p1 & 0xFFFFFFFF, (p0 >> 32) ^ c[3] ^ k[1], p0 & 0xFFFFFFFF]
+        k = [(k[0] + 0x9E3779B9) & 0xFFFFFFFF, (k[1] + 0xBB67AE85) & 0xFFFFFFFF]
+    return c
+
+
+def test_philox_stream_definition(b200):
+    """byte e of the stream = byte e % 16 of Philox4x32-10(key = seed, counter = {e / 16, stream})."""
+
+    assert _philox4x32_10([0xFFFFFFFF] * 4, [0xFFFFFFFF] * 2) == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    dev = torch.device("cuda", 0)
+    seed, stream = 0x0123456789ABCDEF, 0x0FEDCBA987654321
+    key = torch.tensor([seed, stream], dtype=torch.int64, device=dev)
+    raw = b200.PhiloxBits(key).materialize((5 * 16 + 7,)).cpu().numpy()
+    for unit in range(5):
+        words = _philox4x32_10([unit, 0, stream & 0xFFFFFFFF, stream >> 32], [seed & 0xFFFFFFFF, seed >> 32])
+        expect = np.array(words, dtype=np.uint32).view(np.uint8)
+        assert np.array_equal(raw[16 * unit:16 * unit + 16], expect), unit

@@ -146,7 +146,8 @@ __global__ void quantize_row_generic_kernel(const T* __restrict__ x, int64_t row
                 int64_t e = r * cols + c + h;
                 uint32_t rb = 0u;
                 if (stochastic)
-                    rb = bits_dtype == UE5M3_BITS_U8
+                    rb = bits_dtype == UE5M3_BITS_PHILOX ? philox_byte(bits, e)
+                         : bits_dtype == UE5M3_BITS_U8
                              ? static_cast<const uint8_t*>(bits)[e]
                              : (uint32_t)static_cast<const int32_t*>(bits)[e] & 0xFFu;
                 float u = __fmul_rn(load1<T>(x + e), rcp);
@@ -241,7 +242,8 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
                         int64_t e = gr * a.cols + gc + i;
                         v[i] = load1<T>(x + e);
                         if (kSr)
-                            rb[i] = BITS == UE5M3_BITS_U8
+                            rb[i] = BITS == UE5M3_BITS_PHILOX ? philox_byte(a.bits, e)
+                                    : BITS == UE5M3_BITS_U8
                                         ? static_cast<const uint8_t*>(a.bits)[e]
                                         : (uint32_t)static_cast<const int32_t*>(a.bits)[e] & 0xFFu;
                     }
@@ -472,6 +474,11 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ codes, const uint8
     }
 }
 
+__global__ void philox_bytes_kernel(const void* __restrict__ key, int64_t count, uint8_t* __restrict__ out) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (int64_t)gridDim.x * blockDim.x)
+        out[e] = (uint8_t)philox_byte(key, e);
+}
+
 __global__ void alpha_kernel(const float* amax_a, const float* amax_b, float inv_denominator,
                              float* out) {
     out[0] = __fmul_rn(__fmul_rn(amax_a[0], amax_b[0]), inv_denominator);
@@ -535,6 +542,7 @@ static void dispatch_row(int rmode, int bits_dtype, const void* x, int64_t nchun
     launch_row<T, B, R, BT>(x, nchunks, amax_dev, six_t, bits, codes, scales, fake, fake_dtype, fake_domain, stream)
     if (rmode == kRoundSr) {
         if (bits_dtype == UE5M3_BITS_U8) UE5M3_ROW(kRoundSr, UE5M3_BITS_U8);
+        else if (bits_dtype == UE5M3_BITS_PHILOX) UE5M3_ROW(kRoundSr, UE5M3_BITS_PHILOX);
         else UE5M3_ROW(kRoundSr, UE5M3_BITS_I32);
     } else if (rmode == kRoundTteHw) {
         UE5M3_ROW(kRoundTteHw, UE5M3_BITS_U8);
@@ -558,6 +566,7 @@ static int dispatch_tile(int rmode, int bits_dtype, const TileArgs& args, cudaSt
     } while (0)
     if (rmode == kRoundSr) {
         if (bits_dtype == UE5M3_BITS_U8) UE5M3_TILE(kRoundSr, UE5M3_BITS_U8);
+        else if (bits_dtype == UE5M3_BITS_PHILOX) UE5M3_TILE(kRoundSr, UE5M3_BITS_PHILOX);
         else UE5M3_TILE(kRoundSr, UE5M3_BITS_I32);
     } else if (rmode == kRoundTteHw) {
         UE5M3_TILE(kRoundTteHw, UE5M3_BITS_U8);
@@ -586,8 +595,10 @@ static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t col
     if (blocking < UE5M3_BLOCK_ROW || blocking > UE5M3_BLOCK_2D) return UE5M3_ERR_INVALID_ARGUMENT;
     const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
     if (!sr && rounding != UE5M3_ROUND_TIES_TO_EVEN) return UE5M3_ERR_INVALID_ARGUMENT;
-    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_I32)))
+    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_I32 &&
+                         bits_dtype != UE5M3_BITS_PHILOX)))
         return UE5M3_ERR_INVALID_ARGUMENT;
+    if (sr && bits_dtype == UE5M3_BITS_PHILOX && ((uintptr_t)bits % 8)) return UE5M3_ERR_ALIGNMENT;
     if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
     if ((fake || fake_t) && (fake_domain < UE5M3_FAKE_ENCODED || fake_domain > UE5M3_FAKE_DEQUANT ||
                              (fake_dtype != UE5M3_DTYPE_BF16 && fake_dtype != UE5M3_DTYPE_FP32)))
@@ -599,13 +610,13 @@ static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t col
     const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
     const size_t esize = dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
     const bool x_vec = ((uintptr_t)x % 16) == 0 && (cols * esize) % 16 == 0;
-    const bool bits_vec = !sr || (bits_dtype == UE5M3_BITS_U8 ? ((uintptr_t)bits % 8) == 0 && cols % 8 == 0
+    const bool bits_vec = !sr || (bits_dtype == UE5M3_BITS_PHILOX ? cols % 8 == 0 : bits_dtype == UE5M3_BITS_U8 ? ((uintptr_t)bits % 8) == 0 && cols % 8 == 0
                                                               : ((uintptr_t)bits % 16) == 0 && cols % 4 == 0);
     const size_t fsize = fake_dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
 
     if (blocking == UE5M3_BLOCK_ROW) {
         const bool fake_vec = !fake || (((uintptr_t)fake % 16) == 0 && (cols * fsize) % 16 == 0);
-        const bool bits32 = !sr || (bits_dtype == UE5M3_BITS_U8 ? ((uintptr_t)bits % 16) == 0
+        const bool bits32 = !sr || bits_dtype == UE5M3_BITS_PHILOX || (bits_dtype == UE5M3_BITS_U8 ? ((uintptr_t)bits % 16) == 0
                                                                 : ((uintptr_t)bits % 32) == 0);
         const bool fast = cols % block == 0 && x_vec && bits_vec && fake_vec && bits32 &&
                           ((uintptr_t)x % 32) == 0 && (!codes || ((uintptr_t)codes % 8) == 0);
@@ -693,6 +704,14 @@ extern "C" int ue5m3_dequantize(const uint8_t* codes, const uint8_t* scales, int
     int grid = (int)(want < (int64_t)sm_count() * 16 ? want : (int64_t)sm_count() * 16);
     dequantize_kernel<<<grid, 256, 0, stream>>>(codes, scales, rows, cols, block, two_d ? 1 : 0,
                                                 amax_dev, six_t, out, out_dtype);
+    return check_launch();
+}
+
+extern "C" int ue5m3_philox_bytes(const void* seed_stream_dev, int64_t count, uint8_t* out, void* stream_v) {
+    if (!seed_stream_dev || !out || count <= 0 || ((uintptr_t)seed_stream_dev % 8)) return UE5M3_ERR_INVALID_ARGUMENT;
+    int64_t want = (count + 255) / 256;
+    int grid = (int)(want < (int64_t)sm_count() * 16 ? want : (int64_t)sm_count() * 16);
+    philox_bytes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(seed_stream_dev, count, out);
     return check_launch();
 }
 

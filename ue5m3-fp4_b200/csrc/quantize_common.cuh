@@ -48,7 +48,17 @@ __device__ __forceinline__ float load1<float>(const float* p) { return *p; }
 // 8 random bytes -> 8 r14 words.
 template <int BITS>
 __device__ __forceinline__ void load_bits8(const void* bits, int64_t elem, uint32_t (&r14)[8]) {
-    if (BITS == UE5M3_BITS_U8) {
+    if (BITS == UE5M3_BITS_PHILOX) {
+        uint2 seed, stream;
+        philox_load_key(bits, seed, stream);
+        uint32_t r[4];
+        philox_unit(seed, stream, (uint64_t)(elem >> 4), r);  // elem is a multiple of 8
+        const uint32_t lo = (elem & 8) ? r[2] : r[0], hi = (elem & 8) ? r[3] : r[1];
+        r14[0] = r14_from_byte(lo & 0xFFu);         r14[1] = r14_from_byte((lo >> 8) & 0xFFu);
+        r14[2] = r14_from_byte((lo >> 16) & 0xFFu); r14[3] = r14_from_byte(lo >> 24);
+        r14[4] = r14_from_byte(hi & 0xFFu);         r14[5] = r14_from_byte((hi >> 8) & 0xFFu);
+        r14[6] = r14_from_byte((hi >> 16) & 0xFFu); r14[7] = r14_from_byte(hi >> 24);
+    } else if (BITS == UE5M3_BITS_U8) {
         uint2 w = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(bits) + elem));
         r14[0] = r14_from_byte(w.x & 0xFFu);         r14[1] = r14_from_byte((w.x >> 8) & 0xFFu);
         r14[2] = r14_from_byte((w.x >> 16) & 0xFFu); r14[3] = r14_from_byte(w.x >> 24);
@@ -180,7 +190,11 @@ __device__ __forceinline__ void zero_raw_unit(RawUnit<T>& r) {
 // 16 random bytes of one unit, packed four per word
 template <int BITS>
 __device__ __forceinline__ void load_unit_bits(const void* bits, int64_t unit, uint32_t (&r)[4]) {
-    if (BITS == UE5M3_BITS_U8) {
+    if (BITS == UE5M3_BITS_PHILOX) {
+        uint2 seed, stream;
+        philox_load_key(bits, seed, stream);
+        philox_unit(seed, stream, (uint64_t)unit, r);
+    } else if (BITS == UE5M3_BITS_U8) {
         uint4 w = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(bits) + unit * 16));
         r[0] = w.x; r[1] = w.y; r[2] = w.z; r[3] = w.w;
     } else {

@@ -167,6 +167,7 @@ static void dispatch_operand(int rmode, int bits_dtype, const OperandArgs& args,
 #define UE5M3_OP(R, BT) quantize_operand_kernel<T, B, TWO_D, R, BT><<<grid, 256, 0, stream>>>(args)
     if (rmode == kRoundSr) {
         if (bits_dtype == UE5M3_BITS_U8) UE5M3_OP(kRoundSr, UE5M3_BITS_U8);
+        else if (bits_dtype == UE5M3_BITS_PHILOX) UE5M3_OP(kRoundSr, UE5M3_BITS_PHILOX);
         else UE5M3_OP(kRoundSr, UE5M3_BITS_I32);
     } else if (rmode == kRoundTteHw) {
         UE5M3_OP(kRoundTteHw, UE5M3_BITS_U8);
@@ -193,14 +194,16 @@ extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows
     if (blocking != UE5M3_BLOCK_ROW && blocking != UE5M3_BLOCK_2D) return UE5M3_ERR_UNSUPPORTED;
     const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
     if (!sr && rounding != UE5M3_ROUND_TIES_TO_EVEN) return UE5M3_ERR_INVALID_ARGUMENT;
-    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_I32)))
+    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_I32 &&
+                         bits_dtype != UE5M3_BITS_PHILOX)))
         return UE5M3_ERR_INVALID_ARGUMENT;
     if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
     if (sf && (!window_flag || shift < -8 || shift > 16)) return UE5M3_ERR_INVALID_ARGUMENT;
     if (cols % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if (((uintptr_t)x % 32) || ((uintptr_t)codes % 16) || ((uintptr_t)sf % 16) || ((uintptr_t)scales % 4))
         return UE5M3_ERR_ALIGNMENT;
-    if (sr && ((uintptr_t)bits % (bits_dtype == UE5M3_BITS_U8 ? 16 : 32))) return UE5M3_ERR_ALIGNMENT;
+    if (sr && ((uintptr_t)bits % (bits_dtype == UE5M3_BITS_PHILOX ? 8 : bits_dtype == UE5M3_BITS_U8 ? 16 : 32)))
+        return UE5M3_ERR_ALIGNMENT;
 
     OperandArgs args;
     args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;

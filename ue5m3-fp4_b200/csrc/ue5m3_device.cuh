@@ -265,6 +265,42 @@ __device__ __forceinline__ uint32_t e2m1_pack8_sr(const float (&u)[8], uint32_t 
     return magnitude | (signs & 0x88888888u);
 }
 
+// ---- counter-based random bytes (Philox4x32-10) --------------------------------------
+// 16 bytes for the 16-element unit `unit` of the stream {seed, stream}: key = seed,
+// counter = {unit, stream}.  r[j] holds the bytes of elements 4j..4j+3 (lowest byte first).
+__device__ __forceinline__ void philox_unit(uint2 seed, uint2 stream, uint64_t unit, uint32_t (&r)[4]) {
+    uint32_t c0 = (uint32_t)unit, c1 = (uint32_t)(unit >> 32), c2 = stream.x, c3 = stream.y;
+    uint32_t k0 = seed.x, k1 = seed.y;
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        c0 = hi1 ^ c1 ^ k0;
+        c1 = lo1;
+        c2 = hi0 ^ c3 ^ k1;
+        c3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    r[0] = c0; r[1] = c1; r[2] = c2; r[3] = c3;
+}
+
+// {seed, stream} as the kernels read them: two uint64 at `bits`
+__device__ __forceinline__ void philox_load_key(const void* bits, uint2& seed, uint2& stream) {
+    const uint2* p = static_cast<const uint2*>(bits);
+    seed = __ldg(p);
+    stream = __ldg(p + 1);
+}
+
+__device__ __forceinline__ uint32_t philox_byte(const void* bits, int64_t elem) {
+    uint2 seed, stream;
+    philox_load_key(bits, seed, stream);
+    uint32_t r[4];
+    philox_unit(seed, stream, (uint64_t)(elem >> 4), r);
+    const int i = (int)(elem & 15);
+    return (r[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
     return __uint_as_float(bits16 << 16);
 }

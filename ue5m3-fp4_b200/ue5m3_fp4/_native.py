@@ -20,6 +20,7 @@ ROUND_STOCHASTIC_FAST = 7
 BITS_NONE = 0
 BITS_U8 = 1
 BITS_I32 = 2
+BITS_PHILOX = 3
 BLOCK_ROW = 0
 BLOCK_COL = 1
 BLOCK_2D = 2
@@ -79,6 +80,8 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
     lib.ue5m3_quantize_fp4_operand_t.restype = i32
     lib.ue5m3_quantize_fp4_operand_t.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p]
+    lib.ue5m3_philox_bytes.restype = i32
+    lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
     lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, i32, p, i32, i64, p, p]
     lib.ue5m3_test_e2m1_cvt.restype = i32
@@ -117,8 +120,13 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise TypeError(f"unsupported dtype {dtype}; expected bfloat16 or float32")
 
 
-def ptr(tensor: torch.Tensor | None) -> int | None:
-    return None if tensor is None else tensor.data_ptr()
+def ptr(tensor) -> int | None:
+    """Device pointer of a tensor (or of the key tensor of a counter-based bit stream)."""
+
+    if tensor is None:
+        return None
+    key = getattr(tensor, "key", None)
+    return key.data_ptr() if key is not None else tensor.data_ptr()
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -108,9 +108,53 @@ class PackedOperand:
     fake_t: Tensor | None = None  # [cols, rows]
 
 
-def _bits_code(bits: Tensor | None) -> int:
+@dataclass(slots=True)
+class PhiloxBits:
+    """Random bytes that are never materialised: the kernels compute the byte of element e as
+    byte e % 16 of Philox4x32-10(key = seed, counter = {e / 16, stream}).  ``key`` is an int64
+    device tensor {seed, stream}.  The reference draws a bit tensor from a torch generator
+    (nn/linear.py:371-384); its values are not reproducible by any kernel, so parity for this
+    mode is against the explicit bytes returned by ``materialize``."""
+
+    key: Tensor
+
+    @classmethod
+    def draw(cls, device: torch.device, generator: torch.Generator | None = None) -> "PhiloxBits":
+        key = torch.randint(-(2 ** 62), 2 ** 62, (2,), dtype=torch.int64, device=device, generator=generator)
+        return cls(key)
+
+    @property
+    def device(self) -> torch.device:
+        return self.key.device
+
+    def materialize(self, shape) -> Tensor:
+        """The uint8 tensor of this stream for an operand of ``shape`` (row-major elements)."""
+
+        count = 1
+        for extent in shape:
+            count *= int(extent)
+        out = torch.empty(tuple(shape), dtype=torch.uint8, device=self.key.device)
+        with torch.cuda.device(self.key.device):
+            status = _native.load().ue5m3_philox_bytes(self.key.data_ptr(), count, out.data_ptr(),
+                                                       _native.stream_ptr(self.key.device))
+        _native.check(status, "ue5m3_philox_bytes")
+        return out
+
+
+def _check_bits(random_bits, x: Tensor) -> None:
+    if isinstance(random_bits, PhiloxBits):
+        if random_bits.device != x.device or random_bits.key.dtype is not torch.int64 or random_bits.key.numel() != 2:
+            raise ValueError("the Philox key must be two int64 values on the operand's device")
+        return
+    if random_bits.shape != x.shape or random_bits.device != x.device or not random_bits.is_contiguous():
+        raise ValueError("random bits must be contiguous, on the operand's device and of its shape")
+
+
+def _bits_code(bits) -> int:
     if bits is None:
         return _native.BITS_NONE
+    if isinstance(bits, PhiloxBits):
+        return _native.BITS_PHILOX
     if bits.dtype is torch.uint8:
         return _native.BITS_U8
     if bits.dtype is torch.int32:
@@ -154,8 +198,7 @@ def quantize_packed(
     if stochastic:
         if random_bits is None:
             raise ValueError("stochastic rounding requires explicit random bits")
-        if random_bits.shape != x.shape or random_bits.device != x.device or not random_bits.is_contiguous():
-            raise ValueError("random bits must be contiguous, on the operand's device and of its shape")
+        _check_bits(random_bits, x)
     elif random_bits is not None:
         raise ValueError("random bits are only valid with stochastic rounding")
     rows, cols = x.shape
@@ -446,8 +489,7 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
     if stochastic:
         if random_bits is None:
             raise ValueError("stochastic rounding requires explicit random bits")
-        if random_bits.shape != x.shape or random_bits.device != x.device or not random_bits.is_contiguous():
-            raise ValueError("random bits must be contiguous, on the operand's device and of its shape")
+        _check_bits(random_bits, x)
     elif random_bits is not None:
         raise ValueError("random bits are only valid with stochastic rounding")
     dev = x.device

@@ -61,10 +61,19 @@ def _finite_amax(tensor: torch.Tensor) -> torch.Tensor:
     return sample_global_amax(tensor, label="UE5M3 operand amax")
 
 
-def _draw_bits(reference: torch.Tensor) -> torch.Tensor:
-    """One uniform byte per element for StochasticFast rounding (device RNG)."""
+def _draw_bits(reference: torch.Tensor):
+    """One uniform byte per element for StochasticFast rounding.  By default the bytes are a
+    counter-based stream keyed by two draws from the device generator and computed inside the
+    quantizer (no bit tensor is written or read); UE5M3_SR_BITS=tensor materialises a uint8
+    tensor with torch.randint instead (the reference draws an int32 tensor, linear.py:371-384)."""
 
-    return torch.randint(0, 256, reference.shape, dtype=torch.uint8, device=reference.device)
+    import os
+
+    from ue5m3_fp4.backends import b200
+
+    if os.environ.get("UE5M3_SR_BITS", "philox").strip().lower() == "tensor":
+        return torch.randint(0, 256, reference.shape, dtype=torch.uint8, device=reference.device)
+    return b200.PhiloxBits.draw(reference.device)
 
 
 def _reported_quantized_gemm(
