@@ -243,6 +243,11 @@ def test_cta_pair_kernel_is_bit_equal_to_the_single_cta_kernel_and_the_oracle(b2
     (448, 300, 16, "2d", False, torch.float32),
     (128, 96, 32, "2d", False, torch.bfloat16),
     (1024, 1000, 32, "col", True, torch.bfloat16),
+    (320, 208, 16, "col", True, torch.bfloat16),
+    (1024, 1024, 32, "col", True, torch.bfloat16),
+    (256, 160, 16, "col", True, torch.float32),
+    (64, 16, 16, "2d", True, torch.bfloat16),
+    (4096, 1152, 16, "2d", False, torch.bfloat16),
 ])
 def test_one_pass_transposed_operand_equals_quantize_then_pack(b200, k, rows, block, blocking, sr, dtype):
     """ue5m3_quantize_fp4_operand_t (operand = x^T: codes_t + UE4M3 atoms in one launch) against

@@ -545,8 +545,9 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                           (j > 0 || k > 0) ? 1u : 0u, tmem_base + kPTmemSfa + slot * 4,
                                           tmem_base + kPTmemSfb + slot * 8);
                         }
-                        // the stage is free in both CTAs once these MMAs have completed (a relay of
-                        // the leader's barrier through its producer was measured: far slower)
+                        // the stage is free in both CTAs once these MMAs have completed: one commit per
+                        // CTA (a relay through the leader's producer was far slower, a single commit
+                        // addressed to both CTAs no faster)
                         umma_commit_pair(smem_u32(&bars->empty[s]));
                         umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
                     }

@@ -581,6 +581,12 @@ static int dispatch_tile(int rmode, int bits_dtype, const TileArgs& args, cudaSt
 
 using namespace ue5m3;
 
+namespace ue5m3 {
+int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
+                            const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, cudaStream_t stream);
+}
+
 static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t cols, int block,
                              int blocking, const float* amax_dev, float target, int rounding,
                              const void* bits, int bits_dtype, uint8_t* codes, uint8_t* scales,
@@ -685,6 +691,23 @@ extern "C" int ue5m3_quantize_fp4_operand_t(const void* x, int dtype, int64_t ro
     if (blocking != UE5M3_BLOCK_COL && blocking != UE5M3_BLOCK_2D) return UE5M3_ERR_UNSUPPORTED;
     if (rows % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if ((uintptr_t)sf_t % 16) return UE5M3_ERR_ALIGNMENT;
+    if (!x || !amax_dev || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (block != 16 && block != 32) return UE5M3_ERR_BLOCK_SIZE;
+    if (!(target > 0.0f) || !(target < 3.0e38f)) return UE5M3_ERR_INVALID_ARGUMENT;
+    const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
+    if (!sr && rounding != UE5M3_ROUND_TIES_TO_EVEN) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_I32 &&
+                         bits_dtype != UE5M3_BITS_PHILOX)))
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
+    const char* general = getenv("UE5M3_TRANSPOSE_KERNEL");
+    if (!(general && general[0] == '0')) {
+        int fast = quantize_operand_t_fast(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
+                                           bits_dtype, shift, codes_t, sf_t, window_flag,
+                                           static_cast<cudaStream_t>(stream_v));
+        if (fast != UE5M3_ERR_UNSUPPORTED) return fast;
+    }
     return quantize_dispatch(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
                              bits_dtype, nullptr, nullptr, codes_t, nullptr, nullptr, nullptr,
                              UE5M3_DTYPE_BF16, UE5M3_FAKE_NONE, reinterpret_cast<uint32_t*>(sf_t), shift,

@@ -28,46 +28,51 @@ struct OperandArgs {
     int* window_flag;
 };
 
-template <typename T, int B, bool TWO_D, int RMODE, int BITS>
+// U = 16-element units per lane and task: 4 (one whole atom row, 128 input bytes per lane) or
+// 2 (half of it: fewer live registers, more resident warps).
+template <typename T, int B, bool TWO_D, int RMODE, int BITS, int U>
 __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs a) {
+    static_assert(U == 2 || U == 4, "units per task");
     constexpr bool kSr = RMODE == kRoundSr;
     const T* __restrict__ x = static_cast<const T*>(a.x);
     const TensorScale ts = tensor_scale(__ldg(a.amax_dev), a.six_t);
     const int lane = threadIdx.x & 31;
     const int64_t k_atoms = a.cols / 64;
+    const int64_t k_tasks = a.cols / (16 * U);
     const int64_t row_groups = ((a.rows + 127) / 128) * 4;  // 32-row groups, padded to whole atoms
-    const int64_t ntasks = row_groups * k_atoms;
+    const int64_t ntasks = row_groups * k_tasks;
     const int64_t nbc = a.cols / B;
     const int rebias = (8 + a.shift) << 3;
     bool bad = false;
 
     for (int64_t task = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); task < ntasks;
          task += (int64_t)gridDim.x * 8) {
-        const int64_t rg = task / k_atoms, ka = task % k_atoms;
+        const int64_t rg = task / k_tasks, kt = task % k_tasks;
         const int64_t row = rg * 32 + lane;
         const bool valid = row < a.rows;
-        const int64_t unit0 = (row * a.cols + ka * 64) / 16;  // first 16-element unit of this lane
+        const int64_t col0 = kt * (16 * U);
+        const int64_t unit0 = (row * a.cols + col0) / 16;  // first 16-element unit of this lane
 
-        RawUnit<T> raw[4];
-        uint32_t rb[4][4];
+        RawUnit<T> raw[U];
+        uint32_t rb[U][4];
         if (valid) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 load_raw_unit<T>(x, unit0 + u, raw[u]);
                 if (kSr) load_unit_bits<BITS>(a.bits, unit0 + u, rb[u]);
             }
         } else {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 zero_raw_unit<T>(raw[u]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) rb[u][i] = 0u;
             }
         }
 
-        float m[4];
+        float m[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
             float v[16];
             unit_values(raw[u], v);
             m[u] = 0.0f;
@@ -75,25 +80,28 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
             for (int i = 0; i < 16; ++i) m[u] = fmaxf(m[u], fabsf(v[i]));
         }
         if (B == 32) {
-            m[0] = m[1] = fmaxf(m[0], m[1]);
-            m[2] = m[3] = fmaxf(m[2], m[3]);
+#pragma unroll
+            for (int u = 0; u < U; u += 2) m[u] = m[u + 1] = fmaxf(m[u], m[u + 1]);
         }
         if (TWO_D) {
 #pragma unroll
             for (int o = 1; o < B; o <<= 1) {
 #pragma unroll
-                for (int u = 0; u < 4; u += B / 16)
+                for (int u = 0; u < U; u += B / 16)
                     m[u] = fmaxf(m[u], __shfl_xor_sync(0xFFFFFFFFu, m[u], o));
             }
-            if (B == 32) { m[1] = m[0]; m[3] = m[2]; }
+            if (B == 32) {
+#pragma unroll
+                for (int u = 0; u < U; u += 2) m[u + 1] = m[u];
+            }
         }
 
-        uint32_t code[4];
-        uint32_t sf_word = 0u;
-        uint32_t packed[4][2];
+        uint32_t code[U];
+        uint32_t sf_bytes = 0u;
+        uint32_t packed[U][2];
         float scale = 1.0f;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
             if (B == 32 && (u & 1)) {
                 code[u] = code[u - 1];  // same 32-wide block as the previous unit: same scale
             } else {
@@ -104,7 +112,7 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                 bad = bad || valid;
                 code4 = code4 < 8 ? 8 : 0x7E;
             }
-            sf_word |= (uint32_t)code4 << (8 * u);
+            sf_bytes |= (uint32_t)code4 << (8 * u);
             const float rcp = payload_multiplier(scale, ts);
             float v[16];
             unit_values(raw[u], v);
@@ -138,21 +146,36 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
         }
 
         if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(a.codes + row * (a.cols / 2) + ka * 32);
-            dst[0] = make_uint4(packed[0][0], packed[0][1], packed[1][0], packed[1][1]);
-            dst[1] = make_uint4(packed[2][0], packed[2][1], packed[3][0], packed[3][1]);
+            uint4* dst = reinterpret_cast<uint4*>(a.codes + row * (a.cols / 2) + col0 / 2);
+#pragma unroll
+            for (int u = 0; u < U; u += 2)
+                dst[u / 2] = make_uint4(packed[u][0], packed[u][1], packed[u + 1][0], packed[u + 1][1]);
             if (a.scales && (!TWO_D || (row % B) == 0)) {
-                uint8_t* sp = a.scales + (TWO_D ? row / B : row) * nbc + ka * (64 / B);
-                if (B == 16)
-                    *reinterpret_cast<uint32_t*>(sp) = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
-                else
-                    *reinterpret_cast<uint16_t*>(sp) = (uint16_t)(code[0] | (code[2] << 8));
+                uint8_t* sp = a.scales + (TWO_D ? row / B : row) * nbc + col0 / B;
+                if (B == 16) {
+                    if (U == 4)
+                        *reinterpret_cast<uint32_t*>(sp) = code[0] | (code[1] << 8) | (code[2] << 16) | (code[U - 1] << 24);
+                    else
+                        *reinterpret_cast<uint16_t*>(sp) = (uint16_t)(code[0] | (code[1] << 8));
+                } else {
+                    if (U == 4)
+                        *reinterpret_cast<uint16_t*>(sp) = (uint16_t)(code[0] | (code[2] << 8));
+                    else
+                        *sp = (uint8_t)code[0];
+                }
             }
         }
         if (a.sf) {
             const int64_t tile = rg >> 2;
             const int r1 = (int)(rg & 3);
-            a.sf[(tile * k_atoms + ka) * 128 + lane * 4 + r1] = valid ? sf_word : 0x38383838u;
+            const int64_t ka = col0 / 64;
+            uint32_t* word = a.sf + (tile * k_atoms + ka) * 128 + lane * 4 + r1;
+            if (U == 4) {
+                *word = valid ? sf_bytes : 0x38383838u;
+            } else {
+                uint16_t* half = reinterpret_cast<uint16_t*>(word) + (col0 % 64) / 32;
+                *half = valid ? (uint16_t)sf_bytes : (uint16_t)0x3838u;
+            }
         }
     }
     if (bad && a.window_flag) atomicExch(a.window_flag, 1);
@@ -160,11 +183,18 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
 
 template <typename T, int B, bool TWO_D>
 static void dispatch_operand(int rmode, int bits_dtype, const OperandArgs& args, cudaStream_t stream) {
-    const int64_t ntasks = ((args.rows + 127) / 128) * 4 * (args.cols / 64);
+    // ties-to-even fits 64 registers with two units per task (four resident CTAs per SM) and is
+    // then faster; stochastic rounding keeps four (its two-unit form needs 90 registers)
+    const int units = rmode == kRoundSr ? 4 : 2;
+    const int64_t ntasks = ((args.rows + 127) / 128) * 4 * (args.cols / (16 * units));
     const int64_t want = (ntasks + 7) / 8;
     const int64_t cap = (int64_t)sm_count() * 8;
     const int grid = (int)(want < cap ? want : cap);
-#define UE5M3_OP(R, BT) quantize_operand_kernel<T, B, TWO_D, R, BT><<<grid, 256, 0, stream>>>(args)
+#define UE5M3_OP(R, BT)                                                                            \
+    do {                                                                                           \
+        if (units == 2) quantize_operand_kernel<T, B, TWO_D, R, BT, 2><<<grid, 256, 0, stream>>>(args); \
+        else quantize_operand_kernel<T, B, TWO_D, R, BT, 4><<<grid, 256, 0, stream>>>(args);       \
+    } while (0)
     if (rmode == kRoundSr) {
         if (bits_dtype == UE5M3_BITS_U8) UE5M3_OP(kRoundSr, UE5M3_BITS_U8);
         else if (bits_dtype == UE5M3_BITS_PHILOX) UE5M3_OP(kRoundSr, UE5M3_BITS_PHILOX);
@@ -175,6 +205,262 @@ static void dispatch_operand(int rmode, int bits_dtype, const OperandArgs& args,
         UE5M3_OP(kRoundTteSw, UE5M3_BITS_U8);
     }
 #undef UE5M3_OP
+}
+
+
+// ---------------------------------------------------------------------------------------
+// The operand x^T (reduction over the ROWS of x, blocks B x 1 or B x B): a 128 x 128 tile of x
+// goes through shared memory in its storage type (bf16 pairs stay packed), then every lane
+// owns two neighbouring columns and walks down 32 rows, so the per-element work is that of the
+// streaming kernel: no per-element shared-memory staging of results, the codes of a column
+// (32 rows = 16 bytes) and its two scale bytes leave in one store each.
+// Warp w: columns (w & 1) * 64 + 2 * lane + {0, 1}, rows (w >> 1) * 32 .. + 31.
+// ---------------------------------------------------------------------------------------
+constexpr int kTT = 128;                        // tile extent in rows and in columns
+constexpr int kTBitsPitch = kTT + 16;           // bytes per row of the random-byte tile
+
+template <typename T>
+struct TransposeTile {
+    static constexpr int kWordsPerRow = kTT * (int)sizeof(T) / 4;
+    static constexpr int kPitch = kWordsPerRow + 4;  // words; rows stay 16-byte aligned
+};
+
+struct OperandTArgs {
+    const void* x;
+    int64_t rows, cols;   // of x; the operand is [cols, rows]
+    const float* amax_dev;
+    float six_t;
+    const void* bits;
+    uint8_t* codes_t;     // [cols, rows / 2]
+    uint8_t* sf_t;        // atoms of the [cols, rows] operand
+    int shift;
+    int* window_flag;
+};
+
+// two columns x 16 rows from the tile -> values (bf16: one word holds both columns)
+__device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch, int row0, int word, __nv_bfloat16,
+                                                 float (&c0)[16], float (&c1)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t w = tile[(row0 + i) * pitch + word];
+        c0[i] = __uint_as_float(w << 16);
+        c1[i] = __uint_as_float(w & 0xFFFF0000u);
+    }
+}
+
+__device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch, int row0, int word, float,
+                                                 float (&c0)[16], float (&c1)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint2 w = *reinterpret_cast<const uint2*>(&tile[(row0 + i) * pitch + 2 * word]);
+        c0[i] = __uint_as_float(w.x);
+        c1[i] = __uint_as_float(w.y);
+    }
+}
+
+template <typename T, int B, bool TWO_D, int RMODE, int BITS>
+__global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTArgs a) {
+    constexpr bool kSr = RMODE == kRoundSr;
+    constexpr int kPitch = TransposeTile<T>::kPitch;
+    constexpr int kChunksPerRow = TransposeTile<T>::kWordsPerRow / 4;  // 16-byte chunks
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t* tile = reinterpret_cast<uint32_t*>(smem_raw);
+    uint8_t* rbits = smem_raw + (size_t)kTT * kPitch * 4;
+
+    const T* __restrict__ x = static_cast<const T*>(a.x);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t r0 = (int64_t)blockIdx.y * kTT, c0 = (int64_t)blockIdx.x * kTT;
+    const TensorScale ts = tensor_scale(__ldg(a.amax_dev), a.six_t);
+    constexpr int kElemsPerChunk = 16 / (int)sizeof(T);
+
+    // ---- phase 1: global -> shared, rows coalesced, zero padding outside the tensor
+#pragma unroll 4
+    for (int idx = tid; idx < kTT * kChunksPerRow; idx += 256) {
+        const int row = idx / kChunksPerRow, chunk = idx % kChunksPerRow;
+        const int64_t gr = r0 + row, gc = c0 + (int64_t)chunk * kElemsPerChunk;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (gr < a.rows && gc < a.cols) w = __ldg(reinterpret_cast<const uint4*>(x + gr * a.cols + gc));
+        *reinterpret_cast<uint4*>(&tile[row * kPitch + chunk * 4]) = w;
+    }
+    if (kSr) {
+        for (int idx = tid; idx < kTT * (kTT / 16); idx += 256) {
+            const int row = idx / (kTT / 16), unit = idx % (kTT / 16);
+            const int64_t gr = r0 + row, gc = c0 + unit * 16;
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);
+            if (gr < a.rows && gc < a.cols) {
+                const int64_t elem = gr * a.cols + gc;  // a multiple of 16
+                if (BITS == UE5M3_BITS_PHILOX) {
+                    uint2 seed, stream;
+                    philox_load_key(a.bits, seed, stream);
+                    uint32_t r[4];
+                    philox_unit(seed, stream, (uint64_t)(elem >> 4), r);
+                    w = make_uint4(r[0], r[1], r[2], r[3]);
+                } else {
+                    w = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(a.bits) + elem));
+                }
+            }
+            *reinterpret_cast<uint4*>(&rbits[row * kTBitsPitch + unit * 16]) = w;
+        }
+    }
+    __syncthreads();
+
+    // ---- phase 2: lane = two columns, 32 rows
+    const int ch = warp & 1, rq = warp >> 1;
+    const int word = ch * 32 + lane;             // column pair index inside the tile
+    const int row_base = rq * 32;
+    const int64_t col = c0 + 2 * word;           // first of the two columns
+    const int64_t krow = r0 + row_base;          // first reduction index of this warp
+    const bool rows_valid = krow < a.rows;       // rows % 64 == 0: a 32-row quarter is in or out
+
+    float m[2][2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float u0[16], u1[16];
+        tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u0, u1);
+        m[h][0] = m[h][1] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            m[h][0] = fmaxf(m[h][0], fabsf(u0[i]));
+            m[h][1] = fmaxf(m[h][1], fabsf(u1[i]));
+        }
+    }
+    if (B == 32) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) m[0][j] = m[1][j] = fmaxf(m[0][j], m[1][j]);
+    }
+    if (TWO_D) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float v = fmaxf(m[h][0], m[h][1]);
+#pragma unroll
+            for (int o = 1; o < B / 2; o <<= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+            m[h][0] = m[h][1] = v;
+        }
+    }
+
+    const int rebias = (8 + a.shift) << 3;
+    bool bad = false;
+    uint32_t packed[2][4];   // [column][32 rows = 4 words]
+    uint32_t sf_pair[2] = {0u, 0u};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float u[2][16];
+        tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u[0], u[1]);
+        uint32_t rw[2][4];   // random bytes of the 16 rows, per column
+        if (kSr) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t hw[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    hw[i] = *reinterpret_cast<const uint16_t*>(&rbits[(row_base + 16 * h + 4 * q + i) * kTBitsPitch + 2 * word]);
+                const uint32_t p01 = hw[0] | (hw[1] << 16), p23 = hw[2] | (hw[3] << 16);
+                rw[0][q] = __byte_perm(p01, p23, 0x6420u);
+                rw[1][q] = __byte_perm(p01, p23, 0x7531u);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint32_t code;
+            float scale;
+            block_scale_converged(m[h][j], ts, code, scale);
+            int code4 = (int)code - rebias;
+            if (code4 < 8 || code4 > 0x7E) {
+                bad = bad || (rows_valid && col + j < a.cols);
+                code4 = code4 < 8 ? 8 : 0x7E;
+            }
+            sf_pair[j] |= (uint32_t)code4 << (8 * h);
+            const float rcp = payload_multiplier(scale, ts);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) mul2_rn(u[j][i], u[j][i + 1], rcp);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[i] = u[j][half * 8 + i];
+                uint32_t out;
+                if (RMODE == kRoundTteHw) {
+                    out = e2m1_pack8_hw(w);
+                } else if (kSr) {
+                    out = e2m1_pack8_sr(w, rw[j][2 * half], rw[j][2 * half + 1]);
+                } else {
+                    out = 0u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) out += e2m1_nibble<false>(w[i], 0u) * (1u << (4 * i));
+                }
+                packed[j][2 * h + half] = out;
+            }
+        }
+    }
+
+    if (rows_valid) {
+        const int64_t k_atoms = a.rows / 64;
+        const int64_t ka = krow / 64;
+        const int kb0 = (int)((krow % 64) / 16);  // 0 or 2
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int64_t orow = col + j;  // operand row
+            if (orow < a.cols)
+                *reinterpret_cast<uint4*>(a.codes_t + orow * (a.rows / 2) + krow / 2) =
+                    make_uint4(packed[j][0], packed[j][1], packed[j][2], packed[j][3]);
+            // the tile spans one whole 128-row group of the operand: rows beyond `cols` get 1.0
+            uint8_t* word_ptr = a.sf_t + (((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)) * 4;
+            *reinterpret_cast<uint16_t*>(word_ptr + kb0) = orow < a.cols ? (uint16_t)sf_pair[j] : (uint16_t)0x3838u;
+        }
+    }
+    if (bad) atomicExch(a.window_flag, 1);
+}
+
+template <typename T, int B, bool TWO_D>
+static int dispatch_operand_t(int rmode, int bits_dtype, const OperandTArgs& args, cudaStream_t stream) {
+    dim3 grid((unsigned)((args.cols + kTT - 1) / kTT), (unsigned)((args.rows + kTT - 1) / kTT));
+    if (grid.y > 65535u) return UE5M3_ERR_TOO_LARGE;
+    const size_t smem = (size_t)kTT * TransposeTile<T>::kPitch * 4 + (rmode == kRoundSr ? (size_t)kTT * kTBitsPitch : 0);
+#define UE5M3_OPT(R, BT)                                                                         \
+    do {                                                                                         \
+        auto kernel = quantize_operand_t_kernel<T, B, TWO_D, R, BT>;                             \
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        kernel<<<grid, 256, smem, stream>>>(args);                                               \
+    } while (0)
+    if (rmode == kRoundSr) {
+        if (bits_dtype == UE5M3_BITS_PHILOX) UE5M3_OPT(kRoundSr, UE5M3_BITS_PHILOX);
+        else UE5M3_OPT(kRoundSr, UE5M3_BITS_U8);
+    } else if (rmode == kRoundTteHw) {
+        UE5M3_OPT(kRoundTteHw, UE5M3_BITS_U8);
+    } else {
+        UE5M3_OPT(kRoundTteSw, UE5M3_BITS_U8);
+    }
+#undef UE5M3_OPT
+    return UE5M3_OK;
+}
+
+// The transposing kernel takes tensors whose rows are 16-byte multiples; everything else (and
+// int32 bit tensors) stays on the general tile kernel.  Returns UE5M3_ERR_UNSUPPORTED when the
+// caller should use that one.
+int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
+                            const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, cudaStream_t stream) {
+    const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
+    const size_t esize = dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
+    if (((uintptr_t)x % 16) || (cols * esize) % 16 || ((uintptr_t)codes_t % 16) || (rows % 64)) return UE5M3_ERR_UNSUPPORTED;
+    if (sr) {
+        if (bits_dtype == UE5M3_BITS_I32 || cols % 16) return UE5M3_ERR_UNSUPPORTED;
+        if (bits_dtype == UE5M3_BITS_U8 && ((uintptr_t)bits % 16)) return UE5M3_ERR_UNSUPPORTED;
+    }
+    OperandTArgs args;
+    args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;
+    args.six_t = (float)((double)target * 6.0);
+    args.bits = bits; args.codes_t = codes_t; args.sf_t = sf_t; args.shift = shift; args.window_flag = window_flag;
+    const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
+    const bool two_d = blocking == UE5M3_BLOCK_2D;
+    int status;
+#define UE5M3_DOT(T, B) \
+    (two_d ? dispatch_operand_t<T, B, true>(rmode, bits_dtype, args, stream) : dispatch_operand_t<T, B, false>(rmode, bits_dtype, args, stream))
+    if (dtype == UE5M3_DTYPE_BF16) status = block == 16 ? UE5M3_DOT(__nv_bfloat16, 16) : UE5M3_DOT(__nv_bfloat16, 32);
+    else status = block == 16 ? UE5M3_DOT(float, 16) : UE5M3_DOT(float, 32);
+#undef UE5M3_DOT
+    if (status != UE5M3_OK) return status;
+    return check_launch();
 }
 
 }  // namespace ue5m3
