@@ -14,7 +14,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -594,6 +593,21 @@ def run_case(args) -> None:
         alpha = b200.encoded_global_alpha(amax_a, amax_b, TARGET, TARGET)
         for _ in range(args.steps):
             b200.gemm_fp4_operands(qa, qb, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    elif args.case == "linear-step":
+        # forward + backward of one UE5M3Linear of the benchmark shape (launch-list captures)
+        from ue5m3_fp4.nn import UE5M3Linear
+
+        layer = UE5M3Linear(K, N, bias=False, backend="probe_matched", module_name="layers.0.mixer.up_proj",
+                            device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            layer.weight.copy_((0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16))
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(device).requires_grad_(True)
+        dy = (1e-3 * torch.randn(M, N, generator=g)).to(torch.bfloat16).to(device)
+        layer.scale_state.begin_step(1)
+        for _ in range(args.steps):
+            layer.weight.grad = None
+            x.grad = None
+            layer(x).backward(dy)
     else:
         z = torch.randn(M, K, generator=g)
         chi = torch.randn(3, M, K, generator=g).square().sum(0)
@@ -624,7 +638,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize"],
+    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize", "linear-step"],
                         help="run one small kernel case for a profiler capture instead of the benchmark")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
