@@ -157,7 +157,9 @@ def gemm_fixtures(formats, numerics) -> dict[str, np.ndarray]:
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
+    root = Path(sys.argv[1])
     formats, numerics = _reference(root)
     np.savez_compressed(HERE / "quantize_golden.npz", **quantize_fixtures(formats))
     np.savez_compressed(HERE / "gemm_golden.npz", **gemm_fixtures(formats, numerics))
