@@ -178,7 +178,7 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
     x, w = _cpu_sample_inputs(rows, cols)
     probe = _cpu_step(x, w)
     # grow the sample toward the budget (work scales with rows*cols)
-    scale = max(1.0, min(64.0, budget_s / max(probe, 1e-3)))
+    scale = max(1.0, min(400.0, budget_s / max(probe, 1e-3)))
     rows = int(min(M, rows * max(1, int(scale ** 0.5))))
     cols = int(min(N, cols * max(1, int(scale ** 0.5))))
     x, w = _cpu_sample_inputs(rows, cols)
