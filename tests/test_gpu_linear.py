@@ -154,3 +154,44 @@ def test_inference_lifecycle_current_tensor_and_frozen():
     assert provenance["numeric_path"] == "quantized_ue5m3_fp4_probe_matched_k64_issue_rz"
     assert provenance["native_hardware"] is False
     assert controller.counters()["proj"]["activation_frozen_resolutions"] == 1
+
+
+def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monkeypatch):
+    """On the FP4 path the forward saves the packed weight-gradient operand of X (codes +
+    scale atoms) instead of the bf16 activations: same gradients, bit for bit, and less
+    than a third of the bytes held for backward."""
+
+    import ue5m3_fp4.nn.linear as linear_module
+
+    tokens, in_f, out_f = 256, 512, 384
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+        monkeypatch.setenv("UE5M3_SAVE_PACKED_ACTIVATIONS", mode)
+        layer = _layer(in_f, out_f, bias=False, seed=5)
+        layer.scale_state.begin_step(1)
+        draws = []
+
+        def fixed_bits(reference, draws=draws):
+            bits = random_bits(reference.shape, seed=40 + len(draws), dtype=torch.uint8).to(reference.device)
+            draws.append(bits)
+            return bits
+
+        monkeypatch.setattr(linear_module, "_draw_bits", fixed_bits)
+        g = torch.Generator().manual_seed(2)
+        x = torch.randn(tokens, in_f, generator=g).to(torch.bfloat16).cuda().requires_grad_(True)
+        dy = (1e-3 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16).cuda()
+        saved = []
+        with torch.autograd.graph.saved_tensors_hooks(lambda t: (saved.append(t.numel() * t.element_size()), t)[1],
+                                                      lambda t: t):
+            y = layer(x)
+        y.backward(dy)
+        torch.cuda.synchronize()
+        results[mode] = (y.detach().clone(), x.grad.clone(), layer.weight.grad.clone(), sum(saved))
+    for a, b in zip(results["1"][:3], results["0"][:3]):
+        assert torch.equal(a, b)
+    weight_bytes = out_f * in_f * 2
+    packed_extra = results["1"][3] - weight_bytes
+    bf16_extra = results["0"][3] - weight_bytes
+    assert bf16_extra == tokens * in_f * 2
+    assert packed_extra * 3 < bf16_extra

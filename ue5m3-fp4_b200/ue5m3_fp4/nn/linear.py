@@ -61,6 +61,15 @@ def _finite_amax(tensor: torch.Tensor) -> torch.Tensor:
     return sample_global_amax(tensor, label="UE5M3 operand amax")
 
 
+def _save_packed_activations() -> bool:
+    """Save the packed weight-gradient operand of X instead of the bf16 activations
+    (UE5M3_SAVE_PACKED_ACTIVATIONS=0 keeps the bf16 copy, as the reference does)."""
+
+    import os
+
+    return os.environ.get("UE5M3_SAVE_PACKED_ACTIVATIONS", "1").strip() != "0"
+
+
 def _draw_bits(reference: torch.Tensor):
     """One uniform byte per element for StochasticFast rounding.  By default the bytes are a
     counter-based stream keyed by two draws from the device generator and computed inside the
@@ -272,7 +281,21 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         ctx.bias_dtype = bias.dtype if bias is not None else None
         ctx.activation_reference = activation_reference.detach()
         ctx.weight_reference = weight_reference.detach()
-        ctx.save_for_backward(inputs, weight)
+        ctx.input_shape = inputs.shape
+        ctx.packed_activation = None
+        if (plan.path == "fp4" and _save_packed_activations() and ctx.needs_input_grad[1]
+                and x.shape[0] % 64 == 0):  # the weight-gradient GEMM reduces over the tokens
+            # The weight-gradient GEMM reads X^T blocked along the tokens with the SAME held
+            # reference, so its packed operand (0.5625 byte per element) can be made now and
+            # saved instead of the bf16 activations (2 bytes per element); the result is the
+            # operand the backward would have built (the reference re-quantizes a saved bf16
+            # copy, linear.py:346,385-398).
+            xt = _encode_k_major(x, plan=plan, role="activation", reference=activation_reference,
+                                 reduce_over_rows=True, two_dimensional=False)
+            ctx.packed_activation = (xt.shift, xt.rows, xt.k)
+            ctx.save_for_backward(weight, xt.codes, xt.scale_factors)
+        else:
+            ctx.save_for_backward(weight, inputs)
         return output.reshape(*inputs.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -280,11 +303,20 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         owner: UE5M3Linear = ctx.owner
         if owner._inference["active"]:
             raise RuntimeError("Backward is forbidden after FP4 inference is configured")
-        inputs, weight = ctx.saved_tensors
+        from ue5m3_fp4.backends import b200
+
         plan = _OperandPlan(owner)
         two_d = owner.recipe.two_dimensional_weights
+        if ctx.packed_activation is not None:
+            weight, xt_codes, xt_scales = ctx.saved_tensors
+            shift, rows, k = ctx.packed_activation
+            xt_saved = b200.Fp4Operand(xt_codes, xt_scales, shift, rows, k)
+            x = None
+        else:
+            weight, inputs = ctx.saved_tensors
+            xt_saved = None
+            x = inputs.to(torch.bfloat16).reshape(-1, inputs.shape[-1]).contiguous()
         dy = grad_output.to(torch.bfloat16).reshape(-1, grad_output.shape[-1]).contiguous()
-        x = inputs.to(torch.bfloat16).reshape(-1, inputs.shape[-1]).contiguous()
         w = weight.detach().contiguous()
 
         # One held dY amax serves both backward GEMMs; the random bits are drawn per GEMM.
@@ -306,8 +338,9 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         # blocked along M and written transposed, so M is contiguous.
         dyt_enc = _encode_k_major(dy, plan=plan, role="wgrad_upstream_gradient", reference=dy_reference,
                                   reduce_over_rows=True, two_dimensional=False)
-        xt_enc = _encode_k_major(x, plan=plan, role="activation", reference=ctx.activation_reference,
-                                 reduce_over_rows=True, two_dimensional=False)
+        xt_enc = xt_saved if xt_saved is not None else _encode_k_major(
+            x, plan=plan, role="activation", reference=ctx.activation_reference,
+            reduce_over_rows=True, two_dimensional=False)
         grad_weight = _gemm(
             dyt_enc, xt_enc, owner=owner, reference_a=dy_reference, reference_b=ctx.activation_reference,
             target_a=plan.target("wgrad_upstream_gradient"), target_b=plan.target("activation"),
@@ -316,7 +349,7 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         grad_bias = None
         if ctx.has_bias:
             grad_bias = dy.to(torch.float32).sum(dim=0).to(ctx.bias_dtype)
-        return grad_input.reshape_as(inputs), grad_weight, grad_bias, None
+        return grad_input.reshape(ctx.input_shape), grad_weight, grad_bias, None
 
 
 def _fresh_inference_state(generation: int, cleared: bool, entries: int) -> dict[str, Any]:
