@@ -195,3 +195,49 @@ def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monk
     bf16_extra = results["0"][3] - weight_bytes
     assert bf16_extra == tokens * in_f * 2
     assert packed_extra * 3 < bf16_extra
+
+
+def test_frozen_weight_operand_is_built_once_in_inference(monkeypatch):
+    """After the weight scale is frozen the forward operand of W is cached until the parameter
+    is written again; outputs equal those of a layer that quantizes the weight every time."""
+
+    import ue5m3_fp4.nn.linear as linear_module
+    from ue5m3_fp4.scaling import FP4InferenceScalingController
+
+    calls = []
+    original = linear_module._encode_k_major
+
+    def counting(tensor, **kw):
+        calls.append(kw["role"])
+        return original(tensor, **kw)
+
+    monkeypatch.setattr(linear_module, "_encode_k_major", counting)
+    model = torch.nn.Sequential()
+    model.add_module("proj", _layer(256, 128, bias=False, name="proj"))
+    model.eval()
+    controller = FP4InferenceScalingController(model, activation_mode="current_tensor",
+                                               checkpoint_identity={"name": "synthetic"})
+    controller.reset_after_checkpoint_load()
+    controller.calibrate_and_freeze_weights()
+    controller.begin_measurement()
+    x = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        y1 = model(x)
+        y2 = model(x)
+        y3 = model(x * 0.5)
+    assert calls.count("weight") == 1 and calls.count("activation") == 3
+    assert torch.equal(y1, y2)
+    # a fresh layer with the same weights, training-style forward with the same references
+    fresh = _layer(256, 128, bias=False, name="proj")
+    fresh.scale_state.begin_step(1)
+    with torch.no_grad():
+        assert torch.equal(fresh(x), y1)
+    # writing the parameter invalidates the cached operand
+    before = calls.count("weight")
+    with torch.no_grad():
+        model(x)
+        assert calls.count("weight") == before  # still cached
+        model.proj.weight.mul_(0.5)
+        model(x)
+    assert calls.count("weight") == before + 1
+    assert y3.shape == (64, 128)

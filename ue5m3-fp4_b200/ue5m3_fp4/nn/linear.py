@@ -269,8 +269,12 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         two_d = owner.recipe.two_dimensional_weights
         x_enc = _encode_k_major(x, plan=plan, role="activation", reference=activation_reference,
                                 reduce_over_rows=False, two_dimensional=False)
-        w_enc = _encode_k_major(w, plan=plan, role="weight", reference=weight_reference,
-                                reduce_over_rows=False, two_dimensional=two_d)
+        w_enc = owner._packed_frozen_weight(weight, weight_reference, plan) if owner._inference["active"] else None
+        if w_enc is None:
+            w_enc = _encode_k_major(w, plan=plan, role="weight", reference=weight_reference,
+                                    reduce_over_rows=False, two_dimensional=two_d)
+            if owner._inference["active"]:
+                owner._remember_packed_frozen_weight(weight, weight_reference, plan, w_enc)
         output = _gemm(
             x_enc, w_enc, owner=owner, reference_a=activation_reference, reference_b=weight_reference,
             target_a=plan.target("activation"), target_b=plan.target("weight"),
@@ -284,6 +288,7 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         ctx.input_shape = inputs.shape
         ctx.packed_activation = None
         if (plan.path == "fp4" and _save_packed_activations() and ctx.needs_input_grad[1]
+                and owner.__dict__.get("_grad_mode_at_call", True)
                 and x.shape[0] % 64 == 0):  # the weight-gradient GEMM reduces over the tokens
             # The weight-gradient GEMM reads X^T blocked along the tokens with the SAME held
             # reference, so its packed operand (0.5625 byte per element) can be made now and
@@ -468,6 +473,24 @@ class UE5M3Linear(torch.nn.Module):
     def _reference_tensor(value: float, tensor: torch.Tensor) -> torch.Tensor:
         return torch.tensor(value, device=tensor.device, dtype=torch.float32)
 
+    # After checkpoint load the weight and its amax are frozen, so the forward operand of W
+    # (packed codes + scale atoms, or encoded values on the BF16-issue path) is built once and
+    # reused until the parameter is written again; the reference re-quantizes the weight in
+    # every forward (linear.py:549-554,710-718).
+    def _packed_weight_key(self, weight: torch.Tensor, reference: torch.Tensor, plan) -> tuple:
+        return (weight.data_ptr(), weight._version, tuple(weight.shape), weight.dtype,
+                self._inference["frozen_weights"].get("forward.w"), plan.path, plan.block,
+                self.recipe.two_dimensional_weights)
+
+    def _packed_frozen_weight(self, weight: torch.Tensor, reference: torch.Tensor, plan):
+        cached = self.__dict__.get("_packed_weight_cache")
+        if cached is not None and cached[0] == self._packed_weight_key(weight, reference, plan):
+            return cached[1]
+        return None
+
+    def _remember_packed_frozen_weight(self, weight: torch.Tensor, reference: torch.Tensor, plan, operand) -> None:
+        self.__dict__["_packed_weight_cache"] = (self._packed_weight_key(weight, reference, plan), operand)
+
     def _forward_reference(self, role: str, tensor: torch.Tensor) -> torch.Tensor:
         state = self._inference
         if not state["active"]:
@@ -530,6 +553,7 @@ class UE5M3Linear(torch.nn.Module):
                 "the portable decoded-torch reference is a CPU model and is not part of the "
                 "B200 package; use backend='probe_matched' (CUDA, sm_100a)"
             )
+        self.__dict__["_grad_mode_at_call"] = torch.is_grad_enabled()  # forward() itself runs without grad mode
         return _ProbeMatchedUE5M3LinearFunction.apply(inputs, self.weight, self.bias, self)
 
     # ---- post-load inference lifecycle (module protocol of scaling/inference.py:36-46) ----
@@ -539,6 +563,7 @@ class UE5M3Linear(torch.nn.Module):
         cleared = self.scale_state.clear_runtime() if clear_training_state else 0
         self._inference_generation += 1
         self._inference = _fresh_inference_state(self._inference_generation, clear_training_state, cleared)
+        self.__dict__.pop("_packed_weight_cache", None)
         return {
             "generation": self._inference_generation,
             "legacy_training_state_cleared": dict(self._inference["legacy_training_state_cleared"]),
