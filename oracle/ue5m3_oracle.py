@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
         handle.ue5m3o_gemm_issue_rz.argtypes = [p, p, i64, i64, i64, ctypes.c_int, p, p, p]
         handle.ue5m3o_alpha.restype = f32
         handle.ue5m3o_alpha.argtypes = [f32, f32, f32, f32, ctypes.c_int]
+        handle.ue5m3o_rht_b16.restype = ctypes.c_int
+        handle.ue5m3o_rht_b16.argtypes = [p, i64, i64, p]
         handle.ue5m3o_num_threads.restype = ctypes.c_int
         handle.ue5m3o_set_threads.restype = None
         handle.ue5m3o_set_threads.argtypes = [ctypes.c_int]
@@ -97,6 +99,19 @@ def tensor_scales(amax: float, target: float) -> tuple[float, float]:
     dec = ctypes.c_float()
     lib().ue5m3o_tensor_scales(amax, target, ctypes.byref(enc), ctypes.byref(dec))
     return enc.value, dec.value
+
+
+def rht_b16(x: np.ndarray) -> np.ndarray:
+    """Fixed-sign normalized B=16 Hadamard transform along the last axis, BF16 result as fp32
+    (nn/linear.py:80-114 of the reference)."""
+
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if x.ndim != 2 or x.shape[1] % 16:
+        raise ValueError("the B=16 transform expects a rank-2 operand whose last dimension is divisible by 16")
+    out = np.empty_like(x)
+    if lib().ue5m3o_rht_b16(_ptr(x), x.shape[0], x.shape[1], _ptr(out)):
+        raise ValueError("ue5m3o_rht_b16 failed")
+    return out
 
 
 def amax(x: np.ndarray) -> float:

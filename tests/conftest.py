@@ -28,6 +28,11 @@ def gemm_golden():
     return np.load(ROOT / "tests" / "golden" / "gemm_golden.npz")
 
 
+@pytest.fixture(scope="session")
+def rht_golden():
+    return np.load(ROOT / "tests" / "golden" / "rht_golden.npz")
+
+
 def golden_case_names(npz) -> list[str]:
     return sorted({key.split(".")[0] for key in npz.files})
 

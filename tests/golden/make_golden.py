@@ -156,6 +156,29 @@ def gemm_fixtures(formats, numerics) -> dict[str, np.ndarray]:
     return out
 
 
+def rht_fixtures(root: Path) -> dict:
+    """The TE-settings comparator's fixed-sign B=16 Hadamard transform (nn/linear.py:80-114),
+    run on the CPU: seeded inputs and the reference's BF16 outputs."""
+
+    from ue5m3_fp4.nn.linear import _te_settings_rht_last_dim_b16  # noqa: PLC0415
+
+    g = torch.Generator().manual_seed(1234)
+    cases = {
+        "normal": torch.randn(32, 128, generator=g).to(torch.bfloat16).float(),
+        "small": (1e-3 * torch.randn(24, 64, generator=g)).to(torch.bfloat16).float(),
+        "outliers": (torch.randn(16, 96, generator=g)
+                     * torch.where(torch.rand(16, 96, generator=g) < 0.03, 100.0, 1.0)).to(torch.bfloat16).float(),
+        "fp32": torch.randn(8, 64, generator=g),
+        "wide": (torch.randn(16, 64, generator=g)
+                 * torch.exp2(torch.randint(-12, 1, (16, 64), generator=g).float())).to(torch.bfloat16).float(),
+    }
+    out = {"names": np.array(sorted(cases))}
+    for name, x in cases.items():
+        out[f"{name}.x"] = x.numpy()
+        out[f"{name}.y"] = _te_settings_rht_last_dim_b16(x).float().numpy()
+    return out
+
+
 def main() -> None:
     if len(sys.argv) < 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
@@ -163,7 +186,8 @@ def main() -> None:
     formats, numerics = _reference(root)
     np.savez_compressed(HERE / "quantize_golden.npz", **quantize_fixtures(formats))
     np.savez_compressed(HERE / "gemm_golden.npz", **gemm_fixtures(formats, numerics))
-    print("wrote", HERE / "quantize_golden.npz", HERE / "gemm_golden.npz")
+    np.savez_compressed(HERE / "rht_golden.npz", **rht_fixtures(root))
+    print("wrote", HERE / "quantize_golden.npz", HERE / "gemm_golden.npz", HERE / "rht_golden.npz")
 
 
 if __name__ == "__main__":
