@@ -208,6 +208,21 @@ int ue5m3_quantize_fp4_operand_t(const void *x, int dtype, int64_t rows, int64_t
                                  uint8_t *sf_t, int *window_flag, void *stream);
 
 /*
+ * The weight-gradient operands of the TE-settings comparator (nn/linear.py:23-40,80-114,
+ * 389-400): the operand is x^T with the fixed-sign, normalized B=16 Hadamard transform applied
+ * along its reduction axis (the rows of x) before 16 x 1 block quantization.
+ * ue5m3_rht_amax_t writes max |transformed value| (the D=1 reference of the transformed
+ * operand) to amax_out_dev; ue5m3_quantize_fp4_operand_t_rht quantizes with that reference.
+ * rows % 16 == 0 (amax) / rows % 64 == 0 (operand), rows of x 16-byte multiples.
+ */
+int ue5m3_rht_amax_t(const void *x, int dtype, int64_t rows, int64_t cols, float *amax_out_dev,
+                     void *stream);
+int ue5m3_quantize_fp4_operand_t_rht(const void *x, int dtype, int64_t rows, int64_t cols,
+                                     const float *amax_dev, float target, int rounding,
+                                     const void *bits, int bits_dtype, int shift, uint8_t *codes_t,
+                                     uint8_t *sf_t, int *window_flag, void *stream);
+
+/*
  * Probe-matched GEMM on PACKED operands with the FP4 block-scaled tensor cores:
  *   out[M,N] = epilogue( 2^shift_sum * sum over K=64 issues of (A codes x scales) . (B codes x scales) )
  * a_codes [M, K/2], b_codes [N, K/2] (E2M1 nibbles, reduction axis contiguous); a_sf, b_sf from

@@ -275,3 +275,43 @@ def test_one_pass_transposed_operand_equals_quantize_then_pack(b200, k, rows, bl
     assert (op.rows, op.k) == (rows, k)
     assert torch.equal(op.codes, two.codes_t)
     assert torch.equal(op.scale_factors, sf)
+
+
+@pytest.mark.parametrize("k,rows,sr,dtype,wide", [(128, 64, False, torch.bfloat16, False), (320, 208, True, torch.bfloat16, False),
+                                                   (256, 160, False, torch.float32, False), (1024, 384, True, torch.bfloat16, False),
+                                                   (256, 128, False, torch.bfloat16, True)])
+def test_hadamard_transformed_operand_against_the_oracle(b200, k, rows, sr, dtype, wide):
+    """TE-settings comparator: the weight-gradient operand x^T with the fixed-sign B=16 Hadamard
+    transform along the reduction axis, its D=1 amax and its quantization, against the oracle
+    (transform pinned to the reference's function, then the block quantizer)."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(k + rows)
+    x = torch.randn(k, rows, generator=g) * (1e-3 if sr else 1.0)
+    if wide:
+        x = wide_range(k, rows, lo=-10, seed=4)
+    x = x.to(torch.bfloat16).float() if dtype is torch.bfloat16 else x
+    xt_rht = o.rht_b16(np.ascontiguousarray(x.numpy().T))          # [rows, k], transformed along k
+    expect_amax = float(np.abs(xt_rht).max())
+    xd = x.to(dtype).cuda()
+    amax = b200.hadamard_amax_transposed(xd)
+    bits = random_bits((k, rows), k * 3 + rows, torch.uint8) if sr else None
+    b200.window_flag(dev).zero_()
+    op = b200.quantize_fp4_operand(xd, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=amax,
+                                   scale_target=448.0, rounding="StochasticFast" if sr else "TTE",
+                                   random_bits=None if bits is None else bits.cuda(), hadamard=True)
+    torch.cuda.synchronize()
+    # the oracle quantizes the transformed tensor row-wise; its bits are those of x^T
+    ref = expect_packed(oracle_quantize(torch.from_numpy(xt_rht), block=16, blocking=o.BLOCK_ROW, amax=expect_amax,
+                                        target=448.0, sr=sr, bits=None if bits is None else bits.t().contiguous()))
+    if wide:
+        # FP32 butterflies instead of an exact sum: allowed to differ where 16 values span many binades
+        assert abs(float(amax.item()) - expect_amax) <= 2.0 ** -7 * expect_amax
+        assert float((to_np(op.codes) != ref["codes"]).mean()) < 0.01
+        return
+    assert float(amax.item()) == expect_amax
+    assert np.array_equal(to_np(op.codes), ref["codes"])
+    shift = b200.scale_shift_for_target(448.0)
+    sf = b200.pack_scales(torch.from_numpy(ref["scales"]).cuda(), rows=rows, k=k, block_size=16, two_dimensional=False,
+                          shift=shift)
+    assert torch.equal(op.scale_factors, sf)

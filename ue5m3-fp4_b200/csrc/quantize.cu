@@ -584,7 +584,8 @@ using namespace ue5m3;
 namespace ue5m3 {
 int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
                             const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
-                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, cudaStream_t stream);
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, bool rht,
+                            cudaStream_t stream);
 }
 
 static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t cols, int block,
@@ -704,7 +705,7 @@ extern "C" int ue5m3_quantize_fp4_operand_t(const void* x, int dtype, int64_t ro
     const char* general = getenv("UE5M3_TRANSPOSE_KERNEL");
     if (!(general && general[0] == '0')) {
         int fast = quantize_operand_t_fast(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
-                                           bits_dtype, shift, codes_t, sf_t, window_flag,
+                                           bits_dtype, shift, codes_t, sf_t, window_flag, false,
                                            static_cast<cudaStream_t>(stream_v));
         if (fast != UE5M3_ERR_UNSUPPORTED) return fast;
     }

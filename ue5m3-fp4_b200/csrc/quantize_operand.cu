@@ -235,7 +235,36 @@ struct OperandTArgs {
     uint8_t* sf_t;        // atoms of the [cols, rows] operand
     int shift;
     int* window_flag;
+    unsigned int* transformed_amax;  // amax-only mode: max |transformed value| as fp32 bits
 };
+
+// The fixed-sign, normalized B=16 Hadamard transform of the TE-settings comparator
+// (nn/linear.py:23-40,80-114 of the reference) on the 16 consecutive reduction-axis values of
+// one column: y_k = bf16( sum_i bf16(v_i * sign_i) * H[i][k] / 4 ).  The reference runs it as a
+// BF16 matmul (exact products, FP32 accumulation, one rounding to BF16); here the sum is a
+// fast Walsh-Hadamard butterfly in FP32, which is exact unless the 16 values span more than
+// about 12 binades.
+__device__ __forceinline__ void rht16(float (&v)[16]) {
+    constexpr int kNegative = 0xD7E8;  // bit i set: sign_i = -1  (signs 1,1,1,-1,1,-1,-1,-1,-1,-1,-1,1,-1,1,-1,-1)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float x = __bfloat162float(__float2bfloat16_rn(v[i]));
+        v[i] = ((kNegative >> i) & 1) ? -x : x;
+    }
+#pragma unroll
+    for (int len = 1; len < 16; len <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if ((i & len) == 0) {
+                const float a = v[i], b = v[i + len];
+                v[i] = __fadd_rn(a, b);
+                v[i + len] = __fadd_rn(a, -b);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[i], 0.25f)));
+}
 
 // two columns x 16 rows from the tile -> values (bf16: one word holds both columns)
 __device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch, int row0, int word, __nv_bfloat16,
@@ -258,8 +287,9 @@ __device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch
     }
 }
 
-template <typename T, int B, bool TWO_D, int RMODE, int BITS>
+template <typename T, int B, bool TWO_D, int RMODE, int BITS, bool RHT, bool AMAX_ONLY>
 __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTArgs a) {
+    static_assert(!RHT || (B == 16 && !TWO_D), "the transform is defined on 16 x 1 blocks");
     constexpr bool kSr = RMODE == kRoundSr;
     constexpr int kPitch = TransposeTile<T>::kPitch;
     constexpr int kChunksPerRow = TransposeTile<T>::kWordsPerRow / 4;  // 16-byte chunks
@@ -270,7 +300,7 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
     const T* __restrict__ x = static_cast<const T*>(a.x);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t r0 = (int64_t)blockIdx.y * kTT, c0 = (int64_t)blockIdx.x * kTT;
-    const TensorScale ts = tensor_scale(__ldg(a.amax_dev), a.six_t);
+    const TensorScale ts = tensor_scale(AMAX_ONLY ? 1.0f : __ldg(a.amax_dev), a.six_t);
     constexpr int kElemsPerChunk = 16 / (int)sizeof(T);
 
     // ---- phase 1: global -> shared, rows coalesced, zero padding outside the tensor
@@ -317,12 +347,20 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
     for (int h = 0; h < 2; ++h) {
         float u0[16], u1[16];
         tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u0, u1);
+        if (RHT) { rht16(u0); rht16(u1); }
         m[h][0] = m[h][1] = 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             m[h][0] = fmaxf(m[h][0], fabsf(u0[i]));
             m[h][1] = fmaxf(m[h][1], fabsf(u1[i]));
         }
+    }
+    if (AMAX_ONLY) {
+        float v = fmaxf(fmaxf(m[0][0], m[0][1]), fmaxf(m[1][0], m[1][1]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+        if (lane == 0) atomicMax(a.transformed_amax, __float_as_uint(v));  // v >= 0: bit order = value order
+        return;
     }
     if (B == 32) {
 #pragma unroll
@@ -346,6 +384,7 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
     for (int h = 0; h < 2; ++h) {
         float u[2][16];
         tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u[0], u[1]);
+        if (RHT) { rht16(u[0]); rht16(u[1]); }
         uint32_t rw[2][4];   // random bytes of the 16 rows, per column
         if (kSr) {
 #pragma unroll
@@ -411,14 +450,14 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
     if (bad) atomicExch(a.window_flag, 1);
 }
 
-template <typename T, int B, bool TWO_D>
+template <typename T, int B, bool TWO_D, bool RHT>
 static int dispatch_operand_t(int rmode, int bits_dtype, const OperandTArgs& args, cudaStream_t stream) {
     dim3 grid((unsigned)((args.cols + kTT - 1) / kTT), (unsigned)((args.rows + kTT - 1) / kTT));
     if (grid.y > 65535u) return UE5M3_ERR_TOO_LARGE;
     const size_t smem = (size_t)kTT * TransposeTile<T>::kPitch * 4 + (rmode == kRoundSr ? (size_t)kTT * kTBitsPitch : 0);
 #define UE5M3_OPT(R, BT)                                                                         \
     do {                                                                                         \
-        auto kernel = quantize_operand_t_kernel<T, B, TWO_D, R, BT>;                             \
+        auto kernel = quantize_operand_t_kernel<T, B, TWO_D, R, BT, RHT, false>;                 \
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
         kernel<<<grid, 256, smem, stream>>>(args);                                               \
     } while (0)
@@ -439,7 +478,8 @@ static int dispatch_operand_t(int rmode, int bits_dtype, const OperandTArgs& arg
 // caller should use that one.
 int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
                             const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
-                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, cudaStream_t stream) {
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, bool rht,
+                            cudaStream_t stream) {
     const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
     const size_t esize = dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
     if (((uintptr_t)x % 16) || (cols * esize) % 16 || ((uintptr_t)codes_t % 16) || (rows % 64)) return UE5M3_ERR_UNSUPPORTED;
@@ -451,11 +491,19 @@ int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols
     args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;
     args.six_t = (float)((double)target * 6.0);
     args.bits = bits; args.codes_t = codes_t; args.sf_t = sf_t; args.shift = shift; args.window_flag = window_flag;
+    args.transformed_amax = nullptr;
     const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
     const bool two_d = blocking == UE5M3_BLOCK_2D;
     int status;
+    if (rht) {
+        if (block != 16 || two_d) return UE5M3_ERR_INVALID_ARGUMENT;
+        status = dtype == UE5M3_DTYPE_BF16 ? dispatch_operand_t<__nv_bfloat16, 16, false, true>(rmode, bits_dtype, args, stream)
+                                           : dispatch_operand_t<float, 16, false, true>(rmode, bits_dtype, args, stream);
+        if (status != UE5M3_OK) return status;
+        return check_launch();
+    }
 #define UE5M3_DOT(T, B) \
-    (two_d ? dispatch_operand_t<T, B, true>(rmode, bits_dtype, args, stream) : dispatch_operand_t<T, B, false>(rmode, bits_dtype, args, stream))
+    (two_d ? dispatch_operand_t<T, B, true, false>(rmode, bits_dtype, args, stream) : dispatch_operand_t<T, B, false, false>(rmode, bits_dtype, args, stream))
     if (dtype == UE5M3_DTYPE_BF16) status = block == 16 ? UE5M3_DOT(__nv_bfloat16, 16) : UE5M3_DOT(__nv_bfloat16, 32);
     else status = block == 16 ? UE5M3_DOT(float, 16) : UE5M3_DOT(float, 32);
 #undef UE5M3_DOT
@@ -504,4 +552,54 @@ extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows
     else { if (block == 16) UE5M3_DO(float, 16); else UE5M3_DO(float, 32); }
 #undef UE5M3_DO
     return check_launch();
+}
+
+// max |y| over the transformed operand x^T (transform along the rows of x in blocks of 16)
+extern "C" int ue5m3_rht_amax_t(const void* x, int dtype, int64_t rows, int64_t cols, float* amax_out_dev,
+                                void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (!x || !amax_out_dev || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    const size_t esize = dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
+    if (rows % 16) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if (((uintptr_t)x % 16) || (cols * esize) % 16) return UE5M3_ERR_ALIGNMENT;
+    dim3 grid((unsigned)((cols + kTT - 1) / kTT), (unsigned)((rows + kTT - 1) / kTT));
+    if (grid.y > 65535u) return UE5M3_ERR_TOO_LARGE;
+    cudaError_t e = cudaMemsetAsync(amax_out_dev, 0, sizeof(float), stream);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    OperandTArgs args = {};
+    args.x = x; args.rows = rows; args.cols = cols; args.six_t = 1.0f;
+    args.transformed_amax = reinterpret_cast<unsigned int*>(amax_out_dev);
+    if (dtype == UE5M3_DTYPE_BF16) {
+        auto kernel = quantize_operand_t_kernel<__nv_bfloat16, 16, false, kRoundTteHw, UE5M3_BITS_U8, true, true>;
+        const size_t smem = (size_t)kTT * TransposeTile<__nv_bfloat16>::kPitch * 4;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, 256, smem, stream>>>(args);
+    } else {
+        auto kernel = quantize_operand_t_kernel<float, 16, false, kRoundTteHw, UE5M3_BITS_U8, true, true>;
+        const size_t smem = (size_t)kTT * TransposeTile<float>::kPitch * 4;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, 256, smem, stream>>>(args);
+    }
+    return check_launch();
+}
+
+extern "C" int ue5m3_quantize_fp4_operand_t_rht(const void* x, int dtype, int64_t rows, int64_t cols,
+                                                const float* amax_dev, float target, int rounding,
+                                                const void* bits, int bits_dtype, int shift, uint8_t* codes_t,
+                                                uint8_t* sf_t, int* window_flag, void* stream_v) {
+    if (!x || !amax_dev || !codes_t || !sf_t || !window_flag || rows <= 0 || cols <= 0 || shift < -8 || shift > 16)
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!(target > 0.0f) || !(target < 3.0e38f)) return UE5M3_ERR_INVALID_ARGUMENT;
+    const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
+    if (!sr && rounding != UE5M3_ROUND_TIES_TO_EVEN) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_PHILOX))) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (rows % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if ((uintptr_t)sf_t % 16) return UE5M3_ERR_ALIGNMENT;
+    int status = quantize_operand_t_fast(x, dtype, rows, cols, 16, UE5M3_BLOCK_COL, amax_dev, target, rounding, bits,
+                                         bits_dtype, shift, codes_t, sf_t, window_flag, true,
+                                         static_cast<cudaStream_t>(stream_v));
+    return status == UE5M3_ERR_UNSUPPORTED ? UE5M3_ERR_ALIGNMENT : status;
 }

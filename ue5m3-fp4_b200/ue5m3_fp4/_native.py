@@ -80,6 +80,10 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
     lib.ue5m3_quantize_fp4_operand_t.restype = i32
     lib.ue5m3_quantize_fp4_operand_t.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p]
+    lib.ue5m3_rht_amax_t.restype = i32
+    lib.ue5m3_rht_amax_t.argtypes = [p, i32, i64, i64, p, p]
+    lib.ue5m3_quantize_fp4_operand_t_rht.restype = i32
+    lib.ue5m3_quantize_fp4_operand_t_rht.argtypes = [p, i32, i64, i64, p, f32, i32, p, i32, i32, p, p, p, p]
     lib.ue5m3_philox_bytes.restype = i32
     lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32

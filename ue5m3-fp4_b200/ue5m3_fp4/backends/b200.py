@@ -448,12 +448,18 @@ def quantize_fp4_operand(
     rounding: str | RoundingMode = RoundingMode.TIES_TO_EVEN,
     random_bits: Tensor | None = None,
     shift_headroom: int = 0,
+    hadamard: bool = False,
 ) -> Fp4Operand:
     """Quantize ``x`` [R, C] into a packed K-major operand of the FP4 GEMM: reduction over C
     (``transposed=False``: ROW or 2-D blocks) or over R (``transposed=True``: COL or 2-D
     blocks, outputs written transposed)."""
 
     shift = scale_shift_for_target(scale_target) + shift_headroom
+    if hadamard:
+        if not transposed or blocking != BLOCK_COL or block_size != 16:
+            raise ValueError("the fixed-sign B=16 Hadamard transform applies to transposed 16 x 1 operands only")
+        return _quantize_fp4_operand_fused(x, block_size, blocking, tensor_amax, scale_target, rounding,
+                                           random_bits, shift, transposed=True, hadamard=True)
     if not transposed and blocking in (BLOCK_ROW, BLOCK_2D) and x.ndim == 2 and x.shape[1] % 64 == 0 \
             and x.is_contiguous() and x.data_ptr() % 32 == 0:
         return _quantize_fp4_operand_fused(x, block_size, blocking, tensor_amax, scale_target, rounding,
@@ -475,7 +481,7 @@ def quantize_fp4_operand(
 
 def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tensor_amax: Tensor,
                                 scale_target: float, rounding, random_bits: Tensor | None, shift: int,
-                                *, want_scales: bool = False, transposed: bool = False):
+                                *, want_scales: bool = False, transposed: bool = False, hadamard: bool = False):
     """One launch: codes and tensor-core scale atoms (ue5m3_quantize_fp4_operand, or
     ue5m3_quantize_fp4_operand_t for the operand x^T)."""
 
@@ -498,6 +504,18 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
         k, rows = x.shape
         codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
         sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
+        if hadamard:
+            if not x.is_contiguous() or k % 64:
+                raise ValueError("the transformed operand needs a contiguous tensor whose first dimension is a multiple of 64")
+            with torch.cuda.device(dev):
+                status = lib.ue5m3_quantize_fp4_operand_t_rht(
+                    x.data_ptr(), _native.dtype_code(x.dtype), k, rows, tensor_amax.data_ptr(), float(scale_target),
+                    _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
+                    _native.ptr(random_bits), _bits_code(random_bits), shift,
+                    codes.data_ptr(), sf.data_ptr(), window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+                )
+            _native.check(status, "ue5m3_quantize_fp4_operand_t_rht")
+            return Fp4Operand(codes, sf, shift, rows, k)
         with torch.cuda.device(dev):
             status = lib.ue5m3_quantize_fp4_operand_t(
                 x.data_ptr(), _native.dtype_code(x.dtype), k, rows, block_size, blocking,
@@ -527,6 +545,22 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
     _native.check(status, "ue5m3_quantize_fp4_operand")
     operand = Fp4Operand(codes, sf, shift, rows, k)
     return (operand, scales) if want_scales else operand
+
+
+def hadamard_amax_transposed(x: Tensor) -> Tensor:
+    """max |y| (one-element fp32 device tensor) of the operand x^T after the TE-settings
+    comparator's fixed-sign B=16 Hadamard transform along its reduction axis (the rows of x);
+    nn/linear.py:80-114,389-400 of the reference (``_finite_amax`` of the transformed tensor)."""
+
+    _require_cuda(x, "x")
+    if x.ndim != 2 or not x.is_contiguous() or x.shape[0] % 16:
+        raise ValueError("the reported B=16 RHT requires a contiguous rank-2 operand with the reduced dimension divisible by 16")
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        status = _native.load().ue5m3_rht_amax_t(x.data_ptr(), _native.dtype_code(x.dtype), x.shape[0], x.shape[1],
+                                                 out.data_ptr(), _native.stream_ptr(x.device))
+    _native.check(status, "ue5m3_rht_amax_t")
+    return out
 
 
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor | None = None,
