@@ -241,3 +241,59 @@ def test_frozen_weight_operand_is_built_once_in_inference(monkeypatch):
         model(x)
     assert calls.count("weight") == before + 1
     assert y3.shape == (64, 128)
+
+
+def test_te_settings_comparator_backward_matches_oracle(monkeypatch):
+    """UE5M3 with TE settings (D=1, fixed-sign B=16 Hadamard transform on the two weight-gradient
+    operands only): forward and data gradient untransformed, weight gradient on the transformed
+    dY^T and X^T with the amax of the transformed tensors (nn/linear.py:316-324,389-400)."""
+
+    import ue5m3_fp4.nn.linear as linear_module
+    from ue5m3_fp4.backends import b200
+    from ue5m3_fp4.recipe import UE5M3Recipe
+
+    monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+    b200.window_flag(torch.device("cuda", 0)).zero_()  # sticky across calls; earlier tests may have left it set
+    recipe = UE5M3Recipe.transformer_engine_settings()
+    tokens, in_f, out_f = 128, 192, 128
+    name = "layers.7.mixer.up_proj"
+    layer = _layer(in_f, out_f, bias=False, name=name, recipe=recipe, dtype=torch.float32, seed=4)
+    layer.scale_state.begin_step(1)
+    draws = []
+
+    def fixed_bits(reference):
+        bits = random_bits(reference.shape, seed=300 + len(draws), dtype=torch.uint8).to(reference.device)
+        draws.append(bits)
+        return bits
+
+    monkeypatch.setattr(linear_module, "_draw_bits", fixed_bits)
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(tokens, in_f, generator=g).to(torch.bfloat16).cuda().requires_grad_(True)
+    dy = (1e-3 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16).cuda()
+    y = layer(x)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(x.device)
+    assert len(draws) == 2
+
+    w = layer.weight.detach().float().cpu()
+    xh, dyh = x.detach().float().cpu(), dy.float().cpu()
+    ax, aw, ady = float(xh.abs().max()), float(w.abs().max()), float(dyh.abs().max())
+    qx = oracle_quantize(xh, block=16, blocking=o.BLOCK_ROW, amax=ax)
+    qw = oracle_quantize(w, block=16, blocking=o.BLOCK_2D, amax=aw)
+    yo = o.gemm_issue_rz(qx["encoded"], qw["encoded"], snap=True, alpha_value=o.alpha(np.float32(ax), np.float32(aw), 448.0, 448.0))
+    assert np.array_equal(to_np(y), bf16_round(yo))
+    qdy = oracle_quantize(dyh, block=16, blocking=o.BLOCK_ROW, amax=ady, sr=True, bits=draws[0])
+    dxo = o.gemm_issue_rz(qdy["encoded"], np.ascontiguousarray(qw["encoded"].T), snap=True,
+                          alpha_value=o.alpha(np.float32(ady), np.float32(aw), 448.0, 448.0))
+    assert np.array_equal(to_np(x.grad), bf16_round(dxo))
+    # weight gradient: both operands transformed along the tokens, D=1 amax of the transformed tensors
+    dyt = o.rht_b16(np.ascontiguousarray(dyh.numpy().T))
+    xt = o.rht_b16(np.ascontiguousarray(xh.numpy().T))
+    adyt, axt = float(np.abs(dyt).max()), float(np.abs(xt).max())
+    qdyt = oracle_quantize(torch.from_numpy(dyt), block=16, blocking=o.BLOCK_ROW, amax=adyt, sr=True,
+                           bits=draws[1].t().contiguous())
+    qxt = oracle_quantize(torch.from_numpy(xt), block=16, blocking=o.BLOCK_ROW, amax=axt)
+    dwo = o.gemm_issue_rz(qdyt["encoded"], qxt["encoded"], snap=True,
+                          alpha_value=o.alpha(np.float32(adyt), np.float32(axt), 448.0, 448.0))
+    assert np.array_equal(to_np(layer.weight.grad), dwo)

@@ -170,6 +170,7 @@ def _encode_k_major(
     reduce_over_rows: bool,
     two_dimensional: bool,
     bits: torch.Tensor | None = None,
+    hadamard: bool = False,
 ):
     """Quantize ``tensor`` [R, C] into a GEMM operand with the reduction axis contiguous
     ([R, C] when the GEMM reduces over C, [C, R] when it reduces over R; the quantizer writes
@@ -190,7 +191,12 @@ def _encode_k_major(
         return b200.quantize_fp4_operand(
             tensor, block_size=plan.block, blocking=blocking, transposed=reduce_over_rows,
             tensor_amax=reference.reshape(1), scale_target=plan.target(role), rounding=rounding,
-            random_bits=bits, shift_headroom=1,
+            random_bits=bits, shift_headroom=1, hadamard=hadamard,
+        )
+    if hadamard:
+        raise NotImplementedError(
+            "the Hadamard-transformed weight-gradient operands exist on the FP4 tensor-core path only "
+            "(UE5M3_GEMM_PATH=fp4)"
         )
     packed = b200.quantize_packed(
         tensor,
@@ -256,17 +262,25 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
             )
         if weight.dtype not in {torch.bfloat16, torch.float32}:
             raise TypeError("The probe-matched path requires BF16 or FP32 master weights")
-        if owner.recipe.randomized_hadamard_transform:
-            raise NotImplementedError(
-                "the Hadamard-transformed weight-gradient comparator is not built in this package"
-            )
-
         plan = _OperandPlan(owner)
         x = inputs.reshape(-1, inputs.shape[-1]).contiguous()
         w = weight.detach().contiguous()
         activation_reference = owner._forward_reference("activation", x)
         weight_reference = owner._forward_reference("weight", w)
         two_d = owner.recipe.two_dimensional_weights
+        rht = owner.recipe.randomized_hadamard_transform and not owner._inference["active"]
+        activation_rht_reference = None
+        if rht:
+            # The forward GEMM stays untransformed; this current amax belongs to the transformed
+            # X^T that the weight-gradient GEMM reads (linear.py:316-324 of the reference).
+            from ue5m3_fp4.backends import b200
+
+            if plan.path != "fp4":
+                raise NotImplementedError(
+                    "the Hadamard-transformed weight-gradient comparator exists on the FP4 tensor-core "
+                    "path only (UE5M3_GEMM_PATH=fp4)"
+                )
+            activation_rht_reference = _finite_amax(b200.hadamard_amax_transposed(x))
         x_enc = _encode_k_major(x, plan=plan, role="activation", reference=activation_reference,
                                 reduce_over_rows=False, two_dimensional=False)
         w_enc = owner._packed_frozen_weight(weight, weight_reference, plan) if owner._inference["active"] else None
@@ -285,6 +299,7 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         ctx.bias_dtype = bias.dtype if bias is not None else None
         ctx.activation_reference = activation_reference.detach()
         ctx.weight_reference = weight_reference.detach()
+        ctx.activation_rht_reference = None if activation_rht_reference is None else activation_rht_reference.detach()
         ctx.input_shape = inputs.shape
         ctx.packed_activation = None
         if (plan.path == "fp4" and _save_packed_activations() and ctx.needs_input_grad[1]
@@ -295,8 +310,9 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
             # saved instead of the bf16 activations (2 bytes per element); the result is the
             # operand the backward would have built (the reference re-quantizes a saved bf16
             # copy, linear.py:346,385-398).
-            xt = _encode_k_major(x, plan=plan, role="activation", reference=activation_reference,
-                                 reduce_over_rows=True, two_dimensional=False)
+            xt = _encode_k_major(x, plan=plan, role="activation",
+                                 reference=activation_rht_reference if rht else activation_reference,
+                                 reduce_over_rows=True, two_dimensional=False, hadamard=rht)
             ctx.packed_activation = (xt.shift, xt.rows, xt.k)
             ctx.save_for_backward(weight, xt.codes, xt.scale_factors)
         else:
@@ -341,13 +357,23 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
 
         # dW[N,K] = dY^T[N,M] . X[M,K]: reduce over the tokens M; both operands are
         # blocked along M and written transposed, so M is contiguous.
-        dyt_enc = _encode_k_major(dy, plan=plan, role="wgrad_upstream_gradient", reference=dy_reference,
-                                  reduce_over_rows=True, two_dimensional=False)
+        rht = owner.recipe.randomized_hadamard_transform
+        wgrad_dy_reference, wgrad_x_reference = dy_reference, ctx.activation_reference
+        if rht:
+            # The only transformed GEMM of the TE-settings comparator: both operands carry the
+            # fixed-sign B=16 Hadamard transform along the tokens, dY^T with the current amax of
+            # the transformed tensor, X^T with the one sampled in forward (linear.py:389-400).
+            if ctx.activation_rht_reference is None:
+                raise RuntimeError("missing saved transformed-activation amax for RHT wgrad")
+            wgrad_dy_reference = _finite_amax(b200.hadamard_amax_transposed(dy))
+            wgrad_x_reference = ctx.activation_rht_reference
+        dyt_enc = _encode_k_major(dy, plan=plan, role="wgrad_upstream_gradient", reference=wgrad_dy_reference,
+                                  reduce_over_rows=True, two_dimensional=False, hadamard=rht)
         xt_enc = xt_saved if xt_saved is not None else _encode_k_major(
-            x, plan=plan, role="activation", reference=ctx.activation_reference,
-            reduce_over_rows=True, two_dimensional=False)
+            x, plan=plan, role="activation", reference=wgrad_x_reference,
+            reduce_over_rows=True, two_dimensional=False, hadamard=rht)
         grad_weight = _gemm(
-            dyt_enc, xt_enc, owner=owner, reference_a=dy_reference, reference_b=ctx.activation_reference,
+            dyt_enc, xt_enc, owner=owner, reference_a=wgrad_dy_reference, reference_b=wgrad_x_reference,
             target_a=plan.target("wgrad_upstream_gradient"), target_b=plan.target("activation"),
             bias=None, out_dtype=weight.dtype,
         )
