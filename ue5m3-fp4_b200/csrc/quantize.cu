@@ -29,7 +29,7 @@ namespace ue5m3 {
 // B = 16 a thread owns the whole block (no shuffle); with B = 32 two lanes share.
 // ---------------------------------------------------------------------------
 template <typename T, int B, int RMODE, int BITS>
-__global__ void __launch_bounds__(256, RMODE == kRoundSr ? 3 : 4)
+__global__ void __launch_bounds__(256, (RMODE == kRoundSr && sizeof(T) == 4) ? 3 : 4)
 quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __restrict__ amax_dev,
                     float six_t, const void* __restrict__ bits, uint2* __restrict__ codes,
                     uint8_t* __restrict__ scales, void* __restrict__ fake, int fake_dtype,
@@ -39,17 +39,16 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
     const TensorScale ts = tensor_scale(__ldg(amax_dev), six_t);
     const int64_t stride = (int64_t)gridDim.x * (256 * kUnroll);
     for (int64_t base = (int64_t)blockIdx.x * (256 * kUnroll); base < nunits; base += stride) {
-        float v[kUnroll][16];
+        RawUnit<T> raw[kUnroll];
         uint32_t rb[kUnroll][4];
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k) {
             int64_t unit = base + k * 256 + threadIdx.x;
             if (unit < nunits) {
-                load_unit<T>(x, unit, v[k]);
+                load_raw_unit<T>(x, unit, raw[k]);
                 if (RMODE == kRoundSr) load_unit_bits<BITS>(bits, unit, rb[k]);
             } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[k][i] = 0.0f;
+                zero_raw_unit(raw[k]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) rb[k][i] = 0u;
             }
@@ -57,23 +56,25 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k) {
             int64_t unit = base + k * 256 + threadIdx.x;
+            float v[16];
+            unit_values(raw[k], v);
             float m = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[k][i]));
+            for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
             if (kLanesPerBlock == 2) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
             uint32_t code;
             float scale;
             block_scale_converged(m, ts, code, scale);
             const float rcp = payload_multiplier(scale, ts);
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) mul2_rn(v[k][i], v[k][i + 1], rcp);
+            for (int i = 0; i < 16; i += 2) mul2_rn(v[i], v[i + 1], rcp);
             uint32_t packed[2];
             if (RMODE == kRoundTteHw) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float u[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) u[i] = v[k][h * 8 + i];
+                    for (int i = 0; i < 8; ++i) u[i] = v[h * 8 + i];
                     packed[h] = e2m1_pack8_hw(u);
                 }
             } else if (RMODE == kRoundSr) {
@@ -81,8 +82,16 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
                 for (int h = 0; h < 2; ++h) {
                     float u[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) u[i] = v[k][h * 8 + i];
-                    packed[h] = e2m1_pack8_sr(u, rb[k][2 * h], rb[k][2 * h + 1]);
+                    for (int i = 0; i < 8; ++i) u[i] = v[h * 8 + i];
+                    if (sizeof(T) == 2) {
+                        // sign bits straight from the stored bf16 words
+                        uint32_t se, so;
+                        bf16_sign_bytes(raw[k].w[4 * h], raw[k].w[4 * h + 1], raw[k].w[4 * h + 2],
+                                        raw[k].w[4 * h + 3], se, so);
+                        packed[h] = e2m1_pack8_sr_signed(u, rb[k][2 * h], rb[k][2 * h + 1], se, so);
+                    } else {
+                        packed[h] = e2m1_pack8_sr(u, rb[k][2 * h], rb[k][2 * h + 1]);
+                    }
                 }
             } else {
 #pragma unroll
@@ -90,7 +99,7 @@ quantize_row_kernel(const T* __restrict__ x, int64_t nunits, const float* __rest
                     packed[h] = 0u;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        packed[h] += e2m1_nibble<false>(v[k][h * 8 + i], 0u) * (1u << (4 * i));
+                        packed[h] += e2m1_nibble<false>(v[h * 8 + i], 0u) * (1u << (4 * i));
                 }
             }
             if (unit < nunits) {

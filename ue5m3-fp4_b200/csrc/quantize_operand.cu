@@ -31,7 +31,8 @@ struct OperandArgs {
 // U = 16-element units per lane and task: 4 (one whole atom row, 128 input bytes per lane) or
 // 2 (half of it: fewer live registers, more resident warps).
 template <typename T, int B, bool TWO_D, int RMODE, int BITS, int U>
-__global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs a) {
+__global__ void __launch_bounds__(256, RMODE == kRoundTteHw ? 4 : ((RMODE == kRoundSr && sizeof(T) == 2) ? 3 : 2))
+quantize_operand_kernel(const OperandArgs a) {
     static_assert(U == 2 || U == 4, "units per task");
     constexpr bool kSr = RMODE == kRoundSr;
     const T* __restrict__ x = static_cast<const T*>(a.x);
@@ -132,7 +133,15 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
                     float w[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) w[i] = v[h * 8 + i];
-                    packed[u][h] = e2m1_pack8_sr(w, rb[u][2 * h], rb[u][2 * h + 1]);
+                    if (sizeof(T) == 2) {
+                        // sign bits straight from the stored bf16 words
+                        uint32_t se, so;
+                        bf16_sign_bytes(raw[u].w[4 * h], raw[u].w[4 * h + 1], raw[u].w[4 * h + 2],
+                                        raw[u].w[4 * h + 3], se, so);
+                        packed[u][h] = e2m1_pack8_sr_signed(w, rb[u][2 * h], rb[u][2 * h + 1], se, so);
+                    } else {
+                        packed[u][h] = e2m1_pack8_sr(w, rb[u][2 * h], rb[u][2 * h + 1]);
+                    }
                 }
             } else {
 #pragma unroll
@@ -184,7 +193,8 @@ __global__ void __launch_bounds__(256) quantize_operand_kernel(const OperandArgs
 template <typename T, int B, bool TWO_D>
 static void dispatch_operand(int rmode, int bits_dtype, const OperandArgs& args, cudaStream_t stream) {
     // ties-to-even fits 64 registers with two units per task (four resident CTAs per SM) and is
-    // then faster; stochastic rounding keeps four (its two-unit form needs 90 registers)
+    // then faster; stochastic rounding is fastest with four units and three resident CTAs
+    // (80 registers; measured against two units at 64 registers and four at 122)
     const int units = rmode == kRoundSr ? 4 : 2;
     const int64_t ntasks = ((args.rows + 127) / 128) * 4 * (args.cols / (16 * units));
     const int64_t want = (ntasks + 7) / 8;
@@ -288,7 +298,9 @@ __device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch
 }
 
 template <typename T, int B, bool TWO_D, int RMODE, int BITS, bool RHT, bool AMAX_ONLY>
-__global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTArgs a) {
+__global__ void __launch_bounds__(
+    256, RMODE == kRoundTteHw ? 4 : ((RMODE == kRoundSr && sizeof(T) == 2 && B == 16 && !TWO_D && !RHT) ? 3 : 2))
+quantize_operand_t_kernel(const OperandTArgs a) {
     static_assert(!RHT || (B == 16 && !TWO_D), "the transform is defined on 16 x 1 blocks");
     constexpr bool kSr = RMODE == kRoundSr;
     constexpr int kPitch = TransposeTile<T>::kPitch;
@@ -386,6 +398,23 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
         tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u[0], u[1]);
         if (RHT) { rht16(u[0]); rht16(u[1]); }
         uint32_t rw[2][4];   // random bytes of the 16 rows, per column
+        uint32_t sign_even[2][2], sign_odd[2][2];  // [column][half]: sign bytes of rows 0,2,4,6 / 1,3,5,7
+        constexpr bool kRawSigns = kSr && sizeof(T) == 2 && !RHT;
+        if (kRawSigns) {
+            // both columns' sign bits sit in the stored words (bits 15 and 31)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t wr[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) wr[i] = tile[(row_base + 16 * h + 8 * half + i) * kPitch + word];
+                const uint32_t e02 = prmt(wr[0], wr[2], 0xFBD9u), e46 = prmt(wr[4], wr[6], 0xFBD9u);
+                const uint32_t o13 = prmt(wr[1], wr[3], 0xFBD9u), o57 = prmt(wr[5], wr[7], 0xFBD9u);
+                sign_even[0][half] = __byte_perm(e02, e46, 0x5410u);
+                sign_even[1][half] = __byte_perm(e02, e46, 0x7632u);
+                sign_odd[0][half] = __byte_perm(o13, o57, 0x5410u);
+                sign_odd[1][half] = __byte_perm(o13, o57, 0x7632u);
+            }
+        }
         if (kSr) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -420,6 +449,9 @@ __global__ void __launch_bounds__(256) quantize_operand_t_kernel(const OperandTA
                 uint32_t out;
                 if (RMODE == kRoundTteHw) {
                     out = e2m1_pack8_hw(w);
+                } else if (kRawSigns) {
+                    out = e2m1_pack8_sr_signed(w, rw[j][2 * half], rw[j][2 * half + 1], sign_even[j][half],
+                                               sign_odd[j][half]);
                 } else if (kSr) {
                     out = e2m1_pack8_sr(w, rw[j][2 * half], rw[j][2 * half + 1]);
                 } else {

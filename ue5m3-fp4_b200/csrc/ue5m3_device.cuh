@@ -247,7 +247,9 @@ __device__ __forceinline__ uint32_t select_index_bytes(uint32_t h, uint32_t l) {
 
 // Eight scaled inputs -> eight packed nibbles (element 0 lowest), 8-bit-midpoint stochastic
 // rounding; r03 / r47 hold the random bytes of elements 0..3 / 4..7.
-__device__ __forceinline__ uint32_t e2m1_pack8_sr(const float (&u)[8], uint32_t r03, uint32_t r47) {
+// `se` / `so`: per byte 0xFF where element 0,2,4,6 / 1,3,5,7 is negative, else 0x00.
+__device__ __forceinline__ uint32_t e2m1_pack8_sr_signed(const float (&u)[8], uint32_t r03, uint32_t r47,
+                                                         uint32_t se, uint32_t so) {
     uint32_t t[8], s[8];
 #pragma unroll
     for (int i = 0; i < 8; i += 2)
@@ -257,12 +259,26 @@ __device__ __forceinline__ uint32_t e2m1_pack8_sr(const float (&u)[8], uint32_t 
     const uint32_t odd = select_index_bytes(gather_top_bytes(t[1], t[3], t[5], t[7]),
                                             gather_low_bytes_of_magic(s[1], s[3], s[5], s[7]));
     const uint32_t magnitude = even + odd * 16u;  // indices <= 7: no carry between nibbles
+    return magnitude | (se & 0x08080808u) | (so & 0x80808080u);
+}
+
+__device__ __forceinline__ uint32_t e2m1_pack8_sr(const float (&u)[8], uint32_t r03, uint32_t r47) {
     const uint32_t se = gather_sign_bytes(__float_as_uint(u[0]), __float_as_uint(u[2]),
                                           __float_as_uint(u[4]), __float_as_uint(u[6]));
     const uint32_t so = gather_sign_bytes(__float_as_uint(u[1]), __float_as_uint(u[3]),
                                           __float_as_uint(u[5]), __float_as_uint(u[7]));
-    const uint32_t signs = (se & 0x0F0F0F0Fu) | (so & 0xF0F0F0F0u);
-    return magnitude | (signs & 0x88888888u);
+    return e2m1_pack8_sr_signed(u, r03, r47, se, so);
+}
+
+// Sign bytes of eight bf16 elements held in four words (two elements per word, the even one in
+// the low half): four sign-replicating permutes.  Valid where the sign of the scaled value is
+// the sign of the input (every finite input: the multiplier is positive).
+__device__ __forceinline__ void bf16_sign_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
+                                                uint32_t& se, uint32_t& so) {
+    const uint32_t a = prmt(w0, w1, 0xFBD9u);  // signs of elements 0, 2, 1, 3
+    const uint32_t b = prmt(w2, w3, 0xFBD9u);  // signs of elements 4, 6, 5, 7
+    se = __byte_perm(a, b, 0x5410u);
+    so = __byte_perm(a, b, 0x7632u);
 }
 
 // ---- counter-based random bytes (Philox4x32-10) --------------------------------------
