@@ -170,6 +170,56 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
     }
 }
 
+// The same epilogue arithmetic for one warp's 32 rows x 128 columns with BF16 output, stored
+// through a per-warp 32 x 128-byte staging buffer so that every store instruction writes four
+// full 128-byte lines (lane = 16 bytes of a row) instead of 16 bytes in each of 32 rows.
+// 16-byte chunk c of row r sits at chunk position c ^ (r & 7): conflict-free both ways.
+// Requires the whole 128-column half inside N, ldo % 8 == 0 and a 16-byte aligned base.
+constexpr uint32_t kStageBytesPerWarp = 32 * 128;
+
+__device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const uint32_t (&v)[4][32],
+                                                           long long row0, int tile_n, int h, float alpha,
+                                                           unsigned char* stage, int lane) {
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int col0 = tile_n * kFN + h * (kFN / 2) + pass * 64;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t hb[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int idx = pass * 64 + c * 8 + e;
+                float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), p.rescale);
+                if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
+                if (p.alpha) x = __fmul_rn(x, alpha);
+                if (p.bias) {
+                    const int col = col0 + c * 8 + e;
+                    const float bv = p.bias_dtype == UE5M3_DTYPE_BF16
+                                         ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
+                                         : static_cast<const float*>(p.bias)[col];
+                    x = __fadd_rn(x, bv);
+                }
+                hb[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
+            }
+            uint4 w;
+            w.x = hb[0] | (hb[1] << 16); w.y = hb[2] | (hb[3] << 16);
+            w.z = hb[4] | (hb[5] << 16); w.w = hb[6] | (hb[7] << 16);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = w;
+        }
+        __syncwarp();
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+        for (int r4 = 0; r4 < 8; ++r4) {
+            const int r = r4 * 4 + (lane >> 3);
+            const int c = lane & 7;
+            const uint4 w = *reinterpret_cast<const uint4*>(stage + r * 128 + ((c ^ (r & 7)) << 4));
+            const long long row = row0 + r;
+            if (row < p.M) *reinterpret_cast<uint4*>(out + row * p.ldo + col0 + c * 8) = w;
+        }
+        __syncwarp();
+    }
+}
+
 // tile index -> (tile_m, tile_n): groups of 8 tile rows sweep the tile columns together
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tile_m, int& tile_n) {
     constexpr int kGroupM = 8;
@@ -267,6 +317,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             constexpr uint32_t idesc = make_idesc_fp4(kFM, kFN);
             uint32_t g = 0;
             bool ok = true;
+            bool ready = false;  // the current stage's scale barrier was already seen complete
             int it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
                 if (it > 0) {  // the previous tile must have left the accumulator
@@ -278,26 +329,41 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int j = 0; j < num_stages; ++j, ++g) {
                     const int s = g % kFStages;
                     // scales of this stage are in TMEM, which also means its operands have landed
-                    ok = mbar_wait(&bars->sf_full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
-                    ok = __all_sync(0xFFFFFFFFu, ok);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = mbar_wait(&bars->sf_full[s], (g / kFStages) & 1, &bars->abort_flag, p.status, 3, j);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
+                        if (!ok) break;
+                    }
                     tcgen05_fence_after();
+                    // probe the next stage's barrier before the issue (its latency overlaps the issue)
+                    const uint32_t gn = g + 1;
+                    const bool next_ready = mbar_test_wait(&bars->sf_full[gn % kFStages], (gn / kFStages) & 1);
                     const uint32_t sa = smem_u32(smem + s * kFStageBytes);
                     const uint32_t sb = sa + kFBytesA;
                     const uint64_t desc_a = smem_desc_sw128(sa);
                     const uint64_t desc_b = smem_desc_sw128(sb);
+                    const uint32_t t_sfa = tmem_base + kTmemSfa + (uint32_t)s * 16u;
+                    const uint32_t t_sfb = tmem_base + kTmemSfb + (uint32_t)s * 32u;
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    if (elect_one()) {
-                        for (int k = 0; k < issues_here; ++k) {
-                            const uint32_t slot = (uint32_t)(s * 4 + k);
-                            // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
-                            umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                                     (j > 0 || k > 0) ? 1u : 0u, tmem_base + kTmemSfa + slot * 4,
-                                     tmem_base + kTmemSfb + slot * 8);
+                    // 64 four-bit elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                    if (issues_here == 4) {
+                        if (elect_one()) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                         (j > 0 || k > 0) ? 1u : 0u, t_sfa + k * 4, t_sfb + k * 8);
+                            umma_commit(&bars->empty[s]);
                         }
-                        umma_commit(&bars->empty[s]);
+                    } else {
+                        if (elect_one()) {
+                            for (int k = 0; k < issues_here; ++k)
+                                umma_fp4(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                         (j > 0 || k > 0) ? 1u : 0u, t_sfa + k * 4, t_sfb + k * 8);
+                            umma_commit(&bars->empty[s]);
+                        }
                     }
                     __syncwarp();
+                    ready = __all_sync(0xFFFFFFFFu, next_ready);
                 }
                 if (ok && elect_one()) umma_commit(&bars->tmem_full);
                 __syncwarp();
@@ -435,7 +501,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    Fp4PairBarriers* bars = reinterpret_cast<Fp4PairBarriers*>(smem + kPStages * kPStageBytes);
+    unsigned char* stage_base = smem + kPStages * kPStageBytes;  // epilogue staging, 4 KiB per warp
+    Fp4PairBarriers* bars = reinterpret_cast<Fp4PairBarriers*>(stage_base + kFEpilogueWarps * kStageBytesPerWarp);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -517,6 +584,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const uint32_t tmem_full_peer = map_to_cta(smem_u32(&bars->tmem_full), 1);
             uint32_t g = 0;
             bool ok = true;
+            bool ready = false;  // the current stage's scale barrier was already seen complete
             int it = 0;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
                 if (it > 0) {  // both CTAs must have drained the previous tile
@@ -528,30 +596,47 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 }
                 for (int j = 0; j < num_stages; ++j, ++g) {
                     const int s = g % kPStages;
-                    ok = mbar_wait(&bars->sf_full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
-                                   where_base + 3, j);
-                    ok = __all_sync(0xFFFFFFFFu, ok);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = mbar_wait(&bars->sf_full[s], (g / kPStages) & 1, &bars->abort_flag, p.status,
+                                       where_base + 3, j);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
+                        if (!ok) break;
+                    }
                     tcgen05_fence_after();
+                    // look at the next stage's barrier now: the probe's latency then overlaps the
+                    // issue below instead of adding to this thread's time per stage
+                    const uint32_t gn = g + 1;
+                    const bool next_ready = mbar_test_wait(&bars->sf_full[gn % kPStages], (gn / kPStages) & 1);
                     const uint32_t sa = smem_u32(smem + s * kPStageBytes);
                     const uint32_t sb = sa + kPBytesA;
                     const uint64_t desc_a = smem_desc_sw128(sa);
                     const uint64_t desc_b = smem_desc_sw128(sb);
+                    const uint32_t t_sfa = tmem_base + kPTmemSfa + (uint32_t)s * 16u;
+                    const uint32_t t_sfb = tmem_base + kPTmemSfb + (uint32_t)s * 32u;
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    if (elect_one()) {
-                        for (int k = 0; k < issues_here; ++k) {
-                            const uint32_t slot = (uint32_t)(s * 4 + k);
-                            umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                                          (j > 0 || k > 0) ? 1u : 0u, tmem_base + kPTmemSfa + slot * 4,
-                                          tmem_base + kPTmemSfb + slot * 8);
+                    if (issues_here == 4) {
+                        // fixed trip count: the four issues unroll with constant offsets
+                        if (elect_one()) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                              (j > 0 || k > 0) ? 1u : 0u, t_sfa + k * 4, t_sfb + k * 8);
+                            // the stage is free in both CTAs once these MMAs have completed: one
+                            // commit per CTA
+                            umma_commit_pair(smem_u32(&bars->empty[s]));
+                            umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
                         }
-                        // the stage is free in both CTAs once these MMAs have completed: one commit per
-                        // CTA (a relay through the leader's producer was far slower, a single commit
-                        // addressed to both CTAs no faster)
-                        umma_commit_pair(smem_u32(&bars->empty[s]));
-                        umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
+                    } else {
+                        if (elect_one()) {
+                            for (int k = 0; k < issues_here; ++k)
+                                umma_fp4_pair(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                              (j > 0 || k > 0) ? 1u : 0u, t_sfa + k * 4, t_sfb + k * 8);
+                            umma_commit_pair(smem_u32(&bars->empty[s]));
+                            umma_commit_pair(empty_peer0 + (uint32_t)s * 8u);
+                        }
                     }
                     __syncwarp();
+                    ready = __all_sync(0xFFFFFFFFu, next_ready);
                 }
                 if (ok && elect_one()) {
                     umma_commit_pair(smem_u32(&bars->tmem_full));
@@ -576,8 +661,24 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const uint32_t ssfa = smem_u32(smem + s * kPStageBytes) + kPBytesA + kPBytesB;
                     const uint32_t ssfb = ssfa + kFBytesSfa;
                     const int issues_here = (num_issues - 4 * j) < 4 ? (num_issues - 4 * j) : 4;
-                    if (elect_one()) {
-                        for (int k = warp - kFScaleWarp0; k < issues_here; k += kFScaleWarps) {
+                    const int k0 = warp - kFScaleWarp0;
+                    if (issues_here == 4) {
+                        // fixed trip count (two issues per warp): unrolled, constant offsets
+                        if (elect_one()) {
+#pragma unroll
+                            for (int i = 0; i < 4 / kFScaleWarps; ++i) {
+                                const int k = k0 + i * kFScaleWarps;
+                                const uint32_t slot = (uint32_t)(s * 4 + k);
+                                const uint32_t t_sfa = tmem_base + kPTmemSfa + slot * 4;
+                                const uint32_t t_sfb = tmem_base + kPTmemSfb + slot * 8;
+                                tmem_copy_sf_pair(t_sfa, smem_desc_noswizzle_32x16(ssfa + k * kSfAtomBytes));
+                                tmem_copy_sf_pair(t_sfb, smem_desc_noswizzle_32x16(ssfb + k * kSfAtomBytes));
+                                tmem_copy_sf_pair(t_sfb + 4, smem_desc_noswizzle_32x16(ssfb + (4 + k) * kSfAtomBytes));
+                            }
+                            umma_commit_pair(smem_u32(&bars->sf_full[s]));
+                        }
+                    } else if (elect_one()) {
+                        for (int k = k0; k < issues_here; k += kFScaleWarps) {
                             const uint32_t slot = (uint32_t)(s * 4 + k);
                             const uint32_t t_sfa = tmem_base + kPTmemSfa + slot * 4;
                             const uint32_t t_sfb = tmem_base + kPTmemSfb + slot * 8;
@@ -614,7 +715,15 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tmem_empty_leader);
 
-            const long long row = (long long)tile_m * kPM + (long long)rank * 128 + q * 32 + lane;
+            const long long row0 = (long long)tile_m * kPM + (long long)rank * 128 + q * 32;
+            const bool staged = p.out_dtype == UE5M3_DTYPE_BF16 && (p.ldo % 8) == 0 &&
+                                ((uintptr_t)p.out % 16) == 0 && tile_n * kFN + (h + 1) * (kFN / 2) <= p.N;
+            if (staged) {
+                fp4_store_rows_staged_bf16(p, v, row0, tile_n, h, alpha,
+                                           stage_base + (warp - 2) * kStageBytesPerWarp, lane);
+                continue;
+            }
+            const long long row = row0 + lane;
             if (row >= p.M) continue;
             fp4_store_row(p, v, row, tile_n, h, alpha);
         }
@@ -807,7 +916,8 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
         if (status != UE5M3_OK) return status;
         status = make_sf_map(&map_sfb, b_sf, ((N + 127) / 128) * (K / 64));
         if (status != UE5M3_OK) return status;
-        const size_t smem = (size_t)kPStages * kPStageBytes + sizeof(Fp4PairBarriers) + 1024;
+        const size_t smem = (size_t)kPStages * kPStageBytes + kFEpilogueWarps * kStageBytesPerWarp +
+                            sizeof(Fp4PairBarriers) + 1024;
         cudaError_t e = cudaFuncSetAttribute(gemm_fp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return record_cuda_error(e);
         static int max_pairs[64] = {0};

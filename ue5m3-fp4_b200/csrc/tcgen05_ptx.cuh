@@ -47,6 +47,22 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
     return done != 0;
 }
 
+// Non-blocking probe of a phase: true when it has completed.  Used to look at the NEXT stage's
+// barrier before issuing the current stage, so that the probe's latency overlaps the issue.
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // One lane of a converged warp.  Roles that issue TMA / tcgen05 instructions keep their
 // control flow warp-uniform and predicate only the issue on this, so that addresses and
 // descriptors stay in uniform registers.
