@@ -445,7 +445,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // shared memory per CTA instead of 12 KiB.  The leader CTA (rank 0) issues the scale copies,
 // the MMAs and the commits for both; every load of both CTAs reports to the leader's `full`
 // barrier (plain per-CTA TMA loads with cta_group::2, each CTA fetching only its own data).
-// Each CTA drains its own 128 accumulator rows.
+// Each CTA drains its own 128 accumulator rows; BF16 output leaves through a 4 KiB per-warp
+// staging buffer as full 128-byte lines.  The MMA warp's time per stage is what the tensor
+// pipe can be fed at (measured: 128 cycles per MMA when nothing else delays the issue), so its
+// loop is kept short: the four issues of a full stage are unrolled and the next stage's scale
+// barrier is probed before the current issue.
 // ---------------------------------------------------------------------------------------
 constexpr int kPM = 256;
 constexpr int kPStages = 5;
