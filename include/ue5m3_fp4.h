@@ -4,12 +4,16 @@
  * Every entry point takes borrowed DEVICE pointers (unless a parameter says
  * "host"), plain sizes and an explicit CUDA stream (a cudaStream_t passed as
  * void*), launches asynchronously on that stream and returns a status code
- * (UE5M3_OK == 0).  Nothing here allocates or frees device memory; the caller
- * owns every buffer.  The library keeps no global state besides a per-process
- * cache of TMA descriptors encoders (driver entry points).
+ * (UE5M3_OK == 0).  The current device must be the stream's device on every call.
+ * Nothing here allocates or frees device memory; the caller owns every buffer.
+ * Global state of the library: per-process caches of driver entry points (TMA
+ * descriptor encoder) and of per-device attributes (SM count, resident clusters), and,
+ * as the one exception to "the caller owns every buffer", the fixed reduction scratch
+ * of ue5m3_amax_static (a __device__ array per GPU plus a host-side cache of its
+ * address per device ordinal).
  *
- * Each declaration cites the reference interface it replaces, by the file's
- * path inside the reference project.
+ * Each declaration cites the reference interface it replaces, by the file's path
+ * inside the reference project, or says that it has no counterpart there.
  */
 #ifndef UE5M3_FP4_H_
 #define UE5M3_FP4_H_
@@ -21,7 +25,7 @@
 extern "C" {
 #endif
 
-#define UE5M3_ABI_VERSION 1
+#define UE5M3_ABI_VERSION 2
 
 /* status codes */
 #define UE5M3_OK 0
@@ -165,18 +169,39 @@ int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N
                              int *status_dev, void *stream);
 
 /*
+ * Window record of one packed GEMM operand.  The FP4 tensor core takes UE4M3 block scales
+ * (15 binades); UE5M3 spans 32 (formats.py:125-134), so after the per-tensor re-bias a block
+ * scale can fall outside.  Its byte is then clamped in the tensor-core scale atoms, and the
+ * operand ROW that holds it is written into this record, so that ue5m3_gemm_fp4_fallback can
+ * recompute the output rows (A operand) or columns (B operand) it touches.  Layout (int32,
+ * zero-filled by the caller before the operand is quantized):
+ *   [0] number of distinct rows listed (a value > UE5M3_FALLBACK_MAX_ROWS means the list
+ *       overflowed and the whole product is recomputed),
+ *   [1] number of 16-element units whose scale was outside the window (diagnostic),
+ *   [2], [3] reserved,
+ *   [4 .. 4 + UE5M3_FALLBACK_MAX_ROWS) the listed rows, in no particular order,
+ *   [4 + UE5M3_FALLBACK_MAX_ROWS .. + rows) one flag per operand row.
+ * No reference counterpart (the reference has no packed operands and no scale window).
+ */
+#define UE5M3_FALLBACK_MAX_ROWS 1024
+#define UE5M3_WINDOW_RECORD_HEADER 4
+size_t ue5m3_window_record_ints(int64_t operand_rows);
+
+/*
  * UE5M3 scale bytes -> the block-scaled tensor core's UE4M3 scale-factor layout.
  * scales: [rows, K/block] (two_d == 0) or [ceil(rows/block), K/block] (two_d != 0) as written
  * by ue5m3_quantize for a K-major operand.  sf_out: ue5m3_packed_scales_bytes(rows, K) bytes,
  * [ceil(rows/128)][K/64][512]; within a 512-byte atom the byte of row r0 + 32*r1 and 16-block
  * kb sits at r0*16 + r1*4 + kb.  Each byte is the UE5M3 byte minus ((8 + shift) << 3), i.e.
- * the same scale divided by 2^shift in UE4M3; window_flag[0] (device int) is set to 1 when a
- * scale does not fit UE4M3's normal range at that shift.  No reference counterpart (the
- * reference has no packed operands).
+ * the same scale divided by 2^shift in UE4M3, clamped to UE4M3's normal range 0x08..0x7E when
+ * it does not fit; such rows go into window_record (see above).  sf_raw (nullable, same size
+ * and layout) receives the unmodified UE5M3 bytes, which the fallback decodes.
+ * No reference counterpart.
  */
 size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K);
 int ue5m3_pack_scales_ue4m3(const uint8_t *scales, int64_t rows, int64_t K, int block, int two_d,
-                            int shift, uint8_t *sf_out, int *window_flag, void *stream);
+                            int shift, uint8_t *sf_out, uint8_t *sf_raw, int *window_record,
+                            void *stream);
 
 /* count bytes of the UE5M3_BITS_PHILOX stream {seed, stream} starting at element 0 */
 int ue5m3_philox_bytes(const void *seed_stream_dev, int64_t count, uint8_t *out, void *stream);
@@ -186,15 +211,16 @@ int ue5m3_philox_bytes(const void *seed_stream_dev, int64_t count, uint8_t *out,
  * axis of x (blocking UE5M3_BLOCK_ROW or UE5M3_BLOCK_2D; cols = K, K % 64 == 0): same
  * arithmetic as ue5m3_quantize (formats.py:350-457, backends/triton/quantization.py:34-200),
  * writing codes [rows, K/2] and, when sf != NULL, the scales directly in the layout and UE4M3
- * re-bias of ue5m3_pack_scales_ue4m3 (shift, window_flag as there).  scales (optional)
- * receives the raw UE5M3 bytes as ue5m3_quantize would write them.  x 32-byte aligned, codes
+ * re-bias of ue5m3_pack_scales_ue4m3 (shift, sf_raw, window_record as there).  scales
+ * (optional) receives the raw UE5M3 bytes as ue5m3_quantize would write them.  x 32-byte aligned, codes
  * and sf 16-byte aligned.  Operands whose reduction axis is strided (UE5M3_BLOCK_COL,
  * transposed outputs) go through ue5m3_quantize + ue5m3_pack_scales_ue4m3.
  */
 int ue5m3_quantize_fp4_operand(const void *x, int dtype, int64_t rows, int64_t cols, int block,
                                int blocking, const float *amax_dev, float target, int rounding,
                                const void *bits, int bits_dtype, int shift, uint8_t *codes,
-                               uint8_t *sf, uint8_t *scales, int *window_flag, void *stream);
+                               uint8_t *sf, uint8_t *sf_raw, uint8_t *scales, int *window_record,
+                               void *stream);
 
 /*
  * The same for an operand that is x transposed: the reduction axis is the ROW axis of x
@@ -205,7 +231,8 @@ int ue5m3_quantize_fp4_operand(const void *x, int dtype, int64_t rows, int64_t c
 int ue5m3_quantize_fp4_operand_t(const void *x, int dtype, int64_t rows, int64_t cols, int block,
                                  int blocking, const float *amax_dev, float target, int rounding,
                                  const void *bits, int bits_dtype, int shift, uint8_t *codes_t,
-                                 uint8_t *sf_t, int *window_flag, void *stream);
+                                 uint8_t *sf_t, uint8_t *sf_raw_t, int *window_record,
+                                 void *stream);
 
 /*
  * The weight-gradient operands of the TE-settings comparator (nn/linear.py:23-40,80-114,
@@ -220,7 +247,8 @@ int ue5m3_rht_amax_t(const void *x, int dtype, int64_t rows, int64_t cols, float
 int ue5m3_quantize_fp4_operand_t_rht(const void *x, int dtype, int64_t rows, int64_t cols,
                                      const float *amax_dev, float target, int rounding,
                                      const void *bits, int bits_dtype, int shift, uint8_t *codes_t,
-                                     uint8_t *sf_t, int *window_flag, void *stream);
+                                     uint8_t *sf_t, uint8_t *sf_raw_t, int *window_record,
+                                     void *stream);
 
 /*
  * Probe-matched GEMM on PACKED operands with the FP4 block-scaled tensor cores:
@@ -235,6 +263,28 @@ int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
                    const uint8_t *b_sf, int64_t M, int64_t N, int64_t K, int shift_sum, int snap,
                    const float *alpha_dev, const void *bias, int bias_dtype, void *out,
                    int out_dtype, int64_t ldo, int *status_dev, void *stream);
+
+/*
+ * Second half of the FP4 product for operands whose window records are not empty: called
+ * after ue5m3_gemm_fp4 on the same stream with the same epilogue arguments, it overwrites
+ * the output rows listed in a_record and the output columns listed in b_record (everything,
+ * when a list overflowed) with the result of the issue-RZ kernel of ue5m3_gemm_issue_rz_bf16
+ * on the exact encoded operands, which it decodes from the codes and the raw UE5M3 scale
+ * atoms (sf_raw of the quantizers).  The records are read on the device: no host
+ * synchronisation, and with empty records the two launches return at once.  This is what
+ * makes the FP4 path produce the reference model's result for every tensor the reference
+ * accepts (its UE5M3 scales have no window, formats.py:125-134,
+ * backends/triton/quantization.py:116-127).
+ * workspace: ue5m3_gemm_fp4_fallback_workspace_bytes(M, N, K) bytes, 16-byte aligned,
+ * contents undefined before and after.
+ */
+size_t ue5m3_gemm_fp4_fallback_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int ue5m3_gemm_fp4_fallback(const uint8_t *a_codes, const uint8_t *a_sf_raw, const int *a_record,
+                            const uint8_t *b_codes, const uint8_t *b_sf_raw, const int *b_record,
+                            int64_t M, int64_t N, int64_t K, int snap, const float *alpha_dev,
+                            const void *bias, int bias_dtype, void *out, int out_dtype,
+                            int64_t ldo, void *workspace, size_t workspace_bytes,
+                            int *status_dev, void *stream);
 
 /*
  * Test hook: compares the software E2M1 ties-to-even rounding with the sm_100a

@@ -1,6 +1,8 @@
-"""Compile the C oracle into oracle/_build/libue5m3_oracle.so with gcc.
+"""Compile the C oracle into oracle/_build/libue5m3_oracle.so with gcc and, where the reference
+checkout is present, place a copy of its Python package under the git-ignored oracle/_ref/ so
+that the GPU parity tests can run the reference's own Triton kernels as a second oracle.
 
-Test infrastructure only: the shipped package never loads this library.
+Test infrastructure only: the shipped package never loads either.
 """
 
 from __future__ import annotations
@@ -12,9 +14,27 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 SOURCE = HERE / "ue5m3_oracle.c"
 OUTPUT = HERE / "_build" / "libue5m3_oracle.so"
+REFERENCE_PACKAGE = Path(os.environ.get("UE5M3_REFERENCE_ROOT", "/root/reference")) / "src" / "ue5m3_fp4"
+REFERENCE_COPY = HERE / "_ref" / "src"
+
+
+def place_reference_copy() -> Path | None:
+    """oracle/_ref/src/ue5m3_fp4 = the reference's package, unmodified (never committed: the
+    directory is git-ignored).  Returns None when no reference checkout is reachable."""
+
+    import shutil
+
+    if not (REFERENCE_PACKAGE / "backends" / "triton" / "api.py").exists():
+        return REFERENCE_COPY if (REFERENCE_COPY / "ue5m3_fp4").exists() else None
+    target = REFERENCE_COPY / "ue5m3_fp4"
+    if target.exists():
+        shutil.rmtree(target)
+    shutil.copytree(REFERENCE_PACKAGE, target, ignore=shutil.ignore_patterns("__pycache__"))
+    return REFERENCE_COPY
 
 
 def build(force: bool = False) -> Path:
+    place_reference_copy()
     OUTPUT.parent.mkdir(exist_ok=True)
     if (
         not force

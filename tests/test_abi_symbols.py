@@ -35,11 +35,17 @@ def test_library_exports_every_declared_symbol():
 def test_version_and_status_strings():
     lib = ctypes.CDLL(str(_built_library()))
     lib.ue5m3_status_string.restype = ctypes.c_char_p
-    assert lib.ue5m3_abi_version() == 1
+    assert lib.ue5m3_abi_version() == 2
     assert lib.ue5m3_status_string(0) == b"ok"
     assert b"16 or 32" in lib.ue5m3_status_string(2)
     lib.ue5m3_amax_scratch_bytes.restype = ctypes.c_size_t
     assert 4096 <= lib.ue5m3_amax_scratch_bytes() <= 65536
+    lib.ue5m3_window_record_ints.restype = ctypes.c_size_t
+    lib.ue5m3_window_record_ints.argtypes = [ctypes.c_int64]
+    assert lib.ue5m3_window_record_ints(300) == 4 + 1024 + 300
+    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.restype = ctypes.c_size_t
+    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.argtypes = [ctypes.c_int64] * 3
+    assert lib.ue5m3_gemm_fp4_fallback_workspace_bytes(128, 256, 64) == (128 + 256 + 2048) * 64 * 2
 
 
 def test_argument_validation_needs_no_device():

@@ -1,7 +1,8 @@
 """The FP4 block-scaled tensor-core GEMM (ue5m3_gemm_fp4) and its scale packer, through the
-C ABI: scale-factor layout against a numpy restatement, the UE4M3 window flag, bit-exactness
+C ABI: scale-factor layout against a numpy restatement, the window records of scales outside
+UE4M3's range and the recomputation they drive (ue5m3_gemm_fp4_fallback), bit-exactness
 against the oracle on packed operands, equality with the BF16-issue kernel, and the
-benchmark shape on sampled rows x columns."""
+benchmark shapes on sampled rows x columns."""
 
 from __future__ import annotations
 
@@ -43,21 +44,36 @@ def test_scale_packer_layout_and_rebias(b200, rows, k, block, two_d, shift):
     shape = ((rows + block - 1) // block if two_d else rows, k // block)
     lo = (9 + shift) << 3
     scales = torch.randint(lo, lo + 100, shape, generator=g, dtype=torch.int32).to(torch.uint8)
-    b200.window_flag(torch.device("cuda", 0)).zero_()
-    got = b200.pack_scales(scales.cuda(), rows=rows, k=k, block_size=block, two_dimensional=two_d, shift=shift)
+    got, raw, record = b200.pack_scales(scales.cuda(), rows=rows, k=k, block_size=block, two_dimensional=two_d,
+                                        shift=shift, want_raw=True)
     assert np.array_equal(to_np(got), _expected_scale_layout(scales.numpy(), rows, k, block, two_d, shift))
-    assert int(b200.window_flag(got.device).item()) == 0
+    # the raw atoms: same layout, no re-bias (shift -8 makes the restatement subtract nothing), 1.0 = 0x78 padding
+    expect_raw = _expected_scale_layout(scales.numpy(), rows, k, block, two_d, -8)
+    pad = _expected_scale_layout(np.zeros_like(scales.numpy()), rows, k, block, two_d, -8) == 0x38
+    assert np.array_equal(to_np(raw)[~pad], expect_raw[~pad]) and np.all(to_np(raw)[pad] == 0x78)
+    assert record[:2].tolist() == [0, 0]
 
 
-def test_scale_window_flag(b200):
+def test_scale_window_record(b200):
+    """Which UE5M3 bytes fit UE4M3's normal range at shift 0, and what the record then holds."""
+
     dev = torch.device("cuda", 0)
-    for code, expect in [(0x78, 0), ((9 << 3), 0), ((9 << 3) - 1, 1), ((23 << 3) | 6, 0), ((23 << 3) | 7, 1),
-                         (0xF7, 1), (1, 1)]:
-        b200.window_flag(dev).zero_()
-        scales = torch.full((128, 4), code, dtype=torch.uint8, device=dev)
-        b200.pack_scales(scales, rows=128, k=64, block_size=16, two_dimensional=False, shift=0)
-        assert int(b200.window_flag(dev).item()) == expect, hex(code)
-    b200.window_flag(dev).zero_()
+    for code, outside in [(0x78, 0), ((9 << 3), 0), ((9 << 3) - 1, 1), ((23 << 3) | 6, 0), ((23 << 3) | 7, 1),
+                          (0xF7, 1), (1, 1)]:
+        scales = torch.full((128, 4), 0x78, dtype=torch.uint8, device=dev)
+        scales[5, 1] = code
+        scales[77, 0] = code
+        scales[77, 3] = code
+        _, _, record = b200.pack_scales(scales, rows=128, k=64, block_size=16, two_dimensional=False, shift=0,
+                                        want_raw=True)
+        rec = record.tolist()
+        if outside:
+            assert rec[0] == 2 and rec[1] == 3, hex(code)
+            assert sorted(rec[4:6]) == [5, 77]
+            flags = rec[4 + b200.FALLBACK_MAX_ROWS:]
+            assert [i for i, f in enumerate(flags) if f] == [5, 77]
+        else:
+            assert rec[0] == 0 and rec[1] == 0 and not any(rec[4:]), hex(code)
 
 
 def _case(b200, a, bt, *, block, two_d, ta=448.0, tb=448.0, sr=False, held=1.0, seed=0):
@@ -69,7 +85,6 @@ def _case(b200, a, bt, *, block, two_d, ta=448.0, tb=448.0, sr=False, held=1.0, 
     amax_b = float(bt.float().abs().max())
     ta_t = torch.tensor([amax_a], device=dev)
     tb_t = torch.tensor([amax_b], device=dev)
-    b200.window_flag(dev).zero_()
     op_a = b200.quantize_fp4_operand(a.cuda(), block_size=block, blocking=b200.BLOCK_ROW, transposed=False,
                                      tensor_amax=ta_t, scale_target=ta, rounding="StochasticFast" if sr else "TTE",
                                      random_bits=None if bits is None else bits.cuda(),
@@ -133,7 +148,6 @@ def test_probe_matched_falls_back_when_a_scale_leaves_the_window(b200, monkeypat
         results[path] = probe_matched_fp4_gemm(a.cuda(), b.cuda(), block_size=16)
     torch.cuda.synchronize()
     assert torch.equal(results["fp4"], results["bf16"])
-    assert int(b200.window_flag(torch.device("cuda", 0)).item()) == 0  # consumed by the fallback
     qa = oracle_quantize(a.float(), block=16, blocking=o.BLOCK_ROW, amax=float(a.float().abs().max()))
     assert (qa["scale_codes"] < (9 << 3)).any()  # the case does leave the window
 
@@ -146,7 +160,6 @@ def test_fp4_gemm_benchmark_shape_sampled(b200):
     dev = torch.device("cuda", 0)
     xc, wc = x.cuda(), w.cuda()
     ax, aw = b200.tensor_amax(xc).reshape(1), b200.tensor_amax(wc).reshape(1)
-    b200.window_flag(dev).zero_()
     op_a = b200.quantize_fp4_operand(xc, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=ax,
                                      scale_target=448.0)
     op_b = b200.quantize_fp4_operand(wc, block_size=16, blocking=b200.BLOCK_2D, transposed=False, tensor_amax=aw,
@@ -155,6 +168,7 @@ def test_fp4_gemm_benchmark_shape_sampled(b200):
     y = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
+    assert op_a.window_counts() == (0, 0) and op_b.window_counts() == (0, 0)
     rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8063, 8191] + list(range(3000, 3024)))
     col_bands = [0, 240, 256, 10752, 21232, 21488, 7008, 7024]  # whole 16-row bands of W (2-D tiles)
     cols = torch.cat([torch.arange(c, c + 16) for c in col_bands])
@@ -191,32 +205,206 @@ def test_one_pass_operand_quantizer_equals_quantize_then_pack(b200, rows, k, blo
     rounding = "StochasticFast" if sr else "TTE"
     xd = x.to(dtype).cuda()
     bd = None if bits is None else bits.cuda()
-    b200.window_flag(dev).zero_()
     shift = b200.scale_shift_for_target(448.0)
     (op, raw) = b200._quantize_fp4_operand_fused(xd, block, code, amax, 448.0, rounding, bd, shift, want_scales=True)
     two = b200.quantize_packed(xd, block_size=block, blocking=code, tensor_amax=amax, scale_target=448.0,
                                rounding=rounding, random_bits=bd, packed=True, packed_t=False)
-    sf = b200.pack_scales(two.scales, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d", shift=shift)
-    assert int(b200.window_flag(dev).item()) == 0
+    sf, sf_raw, _ = b200.pack_scales(two.scales, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d",
+                                     shift=shift, want_raw=True)
+    assert op.window_counts() == (0, 0)
     assert torch.equal(op.codes, two.codes)
     assert torch.equal(raw, two.scales)
     assert torch.equal(op.scale_factors, sf)
+    assert torch.equal(op.raw_scale_factors, sf_raw)
     ref = expect_packed(oracle_quantize(x, block=block, blocking=code, amax=float(amax.item()), target=448.0,
                                         sr=sr, bits=bits))
     assert np.array_equal(to_np(op.codes), ref["codes"])
     assert np.array_equal(to_np(raw), ref["scales"])
 
 
-def test_one_pass_operand_quantizer_raises_the_window_flag(b200):
+def test_one_pass_operand_quantizers_fill_the_window_record(b200):
     dev = torch.device("cuda", 0)
-    x = torch.ones(128, 64, dtype=torch.bfloat16, device=dev)
-    x[5, 3] = 3.0e4  # every other block's scale falls below the UE4M3 window
+    x = torch.ones(192, 128, dtype=torch.bfloat16, device=dev)
+    x[5, 3] = 3.0e4  # the scale of every block of ones falls below the UE4M3 window
+    x[:, 32:48] = 1.0e3  # except in this band of columns (and the block that holds the maximum)
     amax = torch.tensor([3.0e4], device=dev)
-    b200.window_flag(dev).zero_()
-    b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
-                              scale_target=448.0)
-    assert int(b200.window_flag(dev).item()) == 1
-    b200.window_flag(dev).zero_()
+    op = b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
+                                   scale_target=448.0)
+    assert op.window_counts() == (192, 192 * 7 - 1)
+    assert sorted(op.record[4:4 + 192].tolist()) == list(range(192))
+    # the transposed operand [128, 192]: blocks along the 192 rows of x; only columns 32..47 stay inside
+    op_t = b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=amax,
+                                     scale_target=448.0)
+    listed, units = op_t.window_counts()
+    assert listed == 112 and units == 112 * 12 - 1
+    assert sorted(op_t.record[4:4 + 112].tolist()) == [c for c in range(128) if not 32 <= c < 48]
+
+
+def _bf16_path_product(b200, a, bt, *, block, two_d, amax_a, amax_b, monkeypatch):
+    from ue5m3_fp4.backends.triton import probe_matched_fp4_gemm
+
+    monkeypatch.setenv("UE5M3_GEMM_PATH", "bf16")
+    out = probe_matched_fp4_gemm(a.cuda(), bt.t().contiguous().cuda(), block_size=block, tensor_amax_a=amax_a,
+                                 tensor_amax_b=amax_b, two_dimensional_b=two_d)
+    monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+    return out
+
+
+@pytest.mark.parametrize("m,k,n,block,two_d,out_dtype", [
+    (300, 256, 520, 16, False, torch.float32),
+    (300, 256, 520, 16, False, torch.bfloat16),
+    (256, 512, 384, 32, True, torch.float32),
+    (77, 128, 1030, 16, False, torch.bfloat16),
+])
+def test_rows_and_columns_outside_the_scale_window_are_recomputed(b200, monkeypatch, m, k, n, block, two_d, out_dtype):
+    """A few operand rows of A and of B carry blocks 2^-20 below the rest: their scales leave the
+    UE4M3 window, the records list them, and after ue5m3_gemm_fp4_fallback the whole output
+    equals the BF16-issue product of the same operands bit for bit."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g)
+    bt = torch.randn(n, k, generator=g)
+    rows_a = [0, 31, 130, m - 1]
+    for r in rows_a:
+        a[r, 64:64 + block] *= 2.0 ** -20
+    a = a.to(torch.bfloat16)
+    if two_d:
+        bands_b = [1, (n // block) - 1]
+        for band in bands_b:
+            bt[band * block:(band + 1) * block, 2 * block:3 * block] *= 2.0 ** -20
+        rows_b = [r for band in bands_b for r in range(band * block, (band + 1) * block)]
+    else:
+        rows_b = [3, 255, 256, n - 2]
+        for r in rows_b:
+            bt[r, 0:block] *= 2.0 ** -20
+    bt = bt.to(torch.bfloat16)
+    amax_a = torch.tensor([float(a.float().abs().max())], device=dev)
+    amax_b = torch.tensor([float(bt.float().abs().max())], device=dev)
+    op_a = b200.quantize_fp4_operand(a.cuda(), block_size=block, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=amax_a, scale_target=448.0)
+    op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=block, blocking=b200.BLOCK_2D if two_d else b200.BLOCK_ROW,
+                                     transposed=False, tensor_amax=amax_b, scale_target=448.0)
+    assert sorted(op_a.record[4:4 + len(rows_a)].tolist()) == rows_a and op_a.window_counts()[0] == len(rows_a)
+    assert sorted(op_b.record[4:4 + len(rows_b)].tolist()) == rows_b and op_b.window_counts()[0] == len(rows_b)
+    alpha = b200.encoded_global_alpha(amax_a, amax_b, 448.0, 448.0)
+    bias = torch.randn(n, generator=g).cuda()
+    # the FP4 kernel alone gets the listed rows and columns wrong ...
+    alone = b200.gemm_fp4(op_a.codes, op_a.scale_factors, op_b.codes, op_b.scale_factors, m=m, n=n, k=k,
+                          shift_sum=op_a.shift + op_b.shift, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
+    got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    expect = (_bf16_path_product(b200, a, bt, block=block, two_d=two_d, amax_a=amax_a, amax_b=amax_b,
+                                 monkeypatch=monkeypatch) + bias).to(out_dtype)
+    assert torch.equal(got, expect)
+    wrong = (alone != expect)
+    assert wrong.any()
+    keep_rows = torch.ones(m, dtype=torch.bool, device=dev)
+    keep_rows[rows_a] = False
+    keep_cols = torch.ones(n, dtype=torch.bool, device=dev)
+    keep_cols[rows_b] = False
+    assert not wrong[keep_rows][:, keep_cols].any()  # ... and nothing else
+
+
+def test_an_overflowing_window_record_recomputes_the_whole_product(b200, monkeypatch):
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(12)
+    m, k, n = 1280, 128, 300
+    a = torch.randn(m, k, generator=g)
+    a[:, 16:32] *= 2.0 ** -22  # every row: more rows than a record lists
+    a = a.to(torch.bfloat16)
+    bt = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    amax_a = torch.tensor([float(a.float().abs().max())], device=dev)
+    amax_b = torch.tensor([float(bt.float().abs().max())], device=dev)
+    op_a = b200.quantize_fp4_operand(a.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=amax_a, scale_target=448.0)
+    op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=amax_b, scale_target=448.0)
+    assert op_a.window_counts() == (m, m)
+    alpha = b200.encoded_global_alpha(amax_a, amax_b, 448.0, 448.0)
+    got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    expect = _bf16_path_product(b200, a, bt, block=16, two_d=False, amax_a=amax_a, amax_b=amax_b, monkeypatch=monkeypatch)
+    assert torch.equal(got, expect)
+
+
+def _listed(op) -> list[int]:
+    count = min(op.window_counts()[0], 1024)
+    return sorted(op.record[4:4 + count].tolist())
+
+
+def test_squared_relu_down_proj_at_block_16_forward(b200):
+    """Y = X W^T of an MLP down-projection at its training size: X = relu(z)^2 [8192, 21504], B = 16.
+    A few dozen blocks of X have scales below the UE4M3 window (all sixteen z nearly zero or
+    negative); their rows are listed, recomputed, and, like the other sampled rows, equal the
+    oracle bit for bit."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    m, k, n = 8192, 21504, 4096
+    x = torch.relu(torch.randn(m, k, generator=g)).square().to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    xc, wc = x.cuda(), w.cuda()
+    ax, aw = b200.tensor_amax(xc).reshape(1), b200.tensor_amax(wc).reshape(1)
+    op_a = b200.quantize_fp4_operand(xc, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=ax,
+                                     scale_target=448.0, shift_headroom=1)
+    op_b = b200.quantize_fp4_operand(wc, block_size=16, blocking=b200.BLOCK_2D, transposed=False, tensor_amax=aw,
+                                     scale_target=448.0, shift_headroom=1)
+    alpha = b200.encoded_global_alpha(ax, aw, 448.0, 448.0)
+    y = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    listed = _listed(op_a)
+    print("squared-ReLU forward: rows listed", len(listed), "units outside", op_a.window_counts()[1])
+    assert 0 < len(listed) <= 1024 and op_b.window_counts() == (0, 0)
+    qx_all = oracle_quantize(x[listed].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
+    assert (qx_all["scale_codes"] < (10 << 3)).any(axis=1).all()  # every listed row does leave the window
+    rows = torch.tensor(sorted(set(listed[:24] + [0, 127, 128, 4096, 8191])))
+    col_bands = [0, 256, 2048, 4080]
+    cols = torch.cat([torch.arange(c, c + 16) for c in col_bands])
+    qx = oracle_quantize(x[rows].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
+    enc_w = np.concatenate([
+        oracle_quantize(w[c:c + 16].float(), block=16, blocking=o.BLOCK_2D, amax=float(aw.item()))["encoded"]
+        for c in col_bands
+    ])
+    expect = bf16_round(o.gemm_issue_rz(qx["encoded"], enc_w, snap=True, alpha_value=float(alpha.item())))
+    got = to_np(y[rows.cuda()][:, cols.cuda()])
+    assert np.array_equal(got, expect)
+
+
+def test_squared_relu_down_proj_at_block_16_weight_gradient_operand(b200):
+    """dW = dY^T X of the same layer: the operand X^T is blocked along the tokens, so the blocks
+    below the window now sit in operand rows that are output COLUMNS; they are listed in B's
+    record and recomputed."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(1)
+    tokens, in_f, out_f = 8192, 21504, 1024
+    x = torch.relu(torch.randn(tokens, in_f, generator=g)).square().to(torch.bfloat16)
+    dy = (1e-4 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16)
+    xc, dyc = x.cuda(), dy.cuda()
+    ax, ady = b200.tensor_amax(xc).reshape(1), b200.tensor_amax(dyc).reshape(1)
+    op_a = b200.quantize_fp4_operand(dyc, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=ady,
+                                     scale_target=448.0, shift_headroom=1)
+    op_b = b200.quantize_fp4_operand(xc, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=ax,
+                                     scale_target=448.0, shift_headroom=1)
+    alpha = b200.encoded_global_alpha(ady, ax, 448.0, 448.0)
+    dw = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    listed = _listed(op_b)
+    print("squared-ReLU weight gradient: columns listed", len(listed), "units outside", op_b.window_counts()[1])
+    assert 0 < len(listed) <= 1024 and op_a.window_counts() == (0, 0)
+    cols = torch.tensor(sorted(set(listed[:24] + [0, 255, 256, 21503])))
+    rows = torch.tensor([0, 1, 127, 128, 511, 1023])
+    q_dy = oracle_quantize(dy[:, rows].float(), block=16, blocking=o.BLOCK_COL, amax=float(ady.item()))
+    q_x = oracle_quantize(x[:, cols].float(), block=16, blocking=o.BLOCK_COL, amax=float(ax.item()))
+    expect = bf16_round(o.gemm_issue_rz(np.ascontiguousarray(q_dy["encoded"].T), np.ascontiguousarray(q_x["encoded"].T),
+                                        snap=True, alpha_value=float(alpha.item())))
+    got = to_np(dw[rows.cuda()][:, cols.cuda()])
+    assert np.array_equal(got, expect)
 
 
 @pytest.mark.parametrize("m,k,n,block,two_d", [(256, 256, 256, 16, True), (35, 128, 69, 16, True),
@@ -263,18 +451,18 @@ def test_one_pass_transposed_operand_equals_quantize_then_pack(b200, k, rows, bl
     rounding = "StochasticFast" if sr else "TTE"
     xd = x.to(dtype).cuda()
     bd = None if bits is None else bits.cuda()
-    b200.window_flag(dev).zero_()
     shift = b200.scale_shift_for_target(448.0)
     op = b200.quantize_fp4_operand(xd, block_size=block, blocking=code, transposed=True, tensor_amax=amax,
                                    scale_target=448.0, rounding=rounding, random_bits=bd)
     two = b200.quantize_packed(xd, block_size=block, blocking=code, tensor_amax=amax, scale_target=448.0,
                                rounding=rounding, random_bits=bd, packed=False, packed_t=True)
-    sf = b200.pack_scales(two.scales_t, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d",
-                          shift=shift)
-    assert int(b200.window_flag(dev).item()) == 0
+    sf, sf_raw, _ = b200.pack_scales(two.scales_t, rows=rows, k=k, block_size=block, two_dimensional=blocking == "2d",
+                                     shift=shift, want_raw=True)
+    assert op.window_counts() == (0, 0)
     assert (op.rows, op.k) == (rows, k)
     assert torch.equal(op.codes, two.codes_t)
     assert torch.equal(op.scale_factors, sf)
+    assert torch.equal(op.raw_scale_factors, sf_raw)
 
 
 @pytest.mark.parametrize("k,rows,sr,dtype,wide", [(128, 64, False, torch.bfloat16, False), (320, 208, True, torch.bfloat16, False),
@@ -296,7 +484,6 @@ def test_hadamard_transformed_operand_against_the_oracle(b200, k, rows, sr, dtyp
     xd = x.to(dtype).cuda()
     amax = b200.hadamard_amax_transposed(xd)
     bits = random_bits((k, rows), k * 3 + rows, torch.uint8) if sr else None
-    b200.window_flag(dev).zero_()
     op = b200.quantize_fp4_operand(xd, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=amax,
                                    scale_target=448.0, rounding="StochasticFast" if sr else "TTE",
                                    random_bits=None if bits is None else bits.cuda(), hadamard=True)

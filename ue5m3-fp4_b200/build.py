@@ -13,7 +13,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["abi.cu", "amax.cu", "quantize.cu", "quantize_operand.cu", "gemm_sm100.cu", "gemm_fp4_sm100.cu"]
+SOURCES = ["abi.cu", "amax.cu", "quantize.cu", "quantize_operand.cu", "gemm_sm100.cu", "gemm_fp4_sm100.cu",
+           "gemm_fallback.cu"]
 OUTPUT = HERE / "lib" / "libue5m3_b200.so"
 
 
@@ -31,6 +32,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return OUTPUT
     OUTPUT.parent.mkdir(exist_ok=True)
     objects = []
+    commands = []
     for name in SOURCES:
         obj = OUTPUT.parent / (name + ".o")
         command = [
@@ -43,8 +45,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if verbose:
             command.insert(1, "-Xptxas")
             command.insert(2, "-v")
-        subprocess.run(command, check=True)
+        commands.append(command)
         objects.append(str(obj))
+    if verbose:  # keep each file's ptxas listing together
+        for command in commands:
+            subprocess.run(command, check=True)
+    else:
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=min(len(commands), os.cpu_count() or 1)) as pool:
+            for done in pool.map(lambda c: subprocess.run(c, check=True), commands):
+                done.check_returncode()
     subprocess.run(
         [_nvcc(), "-shared", "-o", str(OUTPUT), *objects, "-gencode", "arch=compute_100a,code=sm_100a"],
         check=True,

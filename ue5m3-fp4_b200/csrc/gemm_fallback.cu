@@ -1,0 +1,492 @@
+// Second half of the FP4 tensor-core product: recomputes, with the issue-RZ BF16 instruction
+// sequence of gemm_sm100.cu, the part of the output that the FP4 kernel could not get right
+// because a UE5M3 block scale fell outside the tensor core's UE4M3 window.
+//
+// The quantizers list such operand rows in a window record (include/ue5m3_fp4.h).  Everything
+// here is driven by those records ON THE DEVICE, so the host launches the same two kernels
+// after every FP4 GEMM without looking at the data:
+//   1. decode_operands_kernel: E2M1 codes x raw UE5M3 scale atoms -> encoded bf16 values
+//      (p * s is exact in bf16).  Listed rows of A go to a compact [1024, K] buffer, and then B
+//      is decoded in full, because a listed output row needs every column; the same with the
+//      roles swapped for listed rows of B (= output columns).
+//   2. gemm_fallback_kernel: persistent CTAs walk the tiles of up to three products,
+//      (listed A rows) x B -> scattered to those output rows, A x (listed B rows) -> scattered
+//      to those output columns, or, when a list overflowed, A x B over the whole output.
+//      Per tile it is the kernel of gemm_sm100.cu: TMA -> 4-stage ring -> four K=16 BF16 MMAs
+//      into a fresh TMEM accumulator per K=64 issue -> round-toward-zero adds in registers ->
+//      snap, alpha, bias, cast.  The issue counter runs on across tiles, so the mbarrier
+//      phases never need re-initialising.
+// With empty records both kernels return after reading two integers.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "abi_common.cuh"
+#include "tcgen05_ptx.cuh"
+#include "ue5m3_device.cuh"
+#include "window_record.cuh"
+
+namespace ue5m3 {
+
+using namespace ptx;
+
+namespace fb {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kStageBytesA = kBM * kBK * 2;
+constexpr uint32_t kStageBytesB = kBN * kBK * 2;
+constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
+
+struct Plan {
+    int na, nb;        // listed rows of A / of B, clamped to the capacity
+    bool full;         // a list overflowed: recompute everything
+    int tiles[3];      // tiles of the row pass, the column pass, the full pass
+};
+
+__device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, int M, int N) {
+    Plan plan;
+    const int na = rec_a ? __ldg(rec_a) : 0, nb = rec_b ? __ldg(rec_b) : 0;
+    plan.full = na > kRecMaxRows || nb > kRecMaxRows;
+    plan.na = plan.full ? 0 : na;
+    plan.nb = plan.full ? 0 : nb;
+    const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + kBN - 1) / kBN;
+    plan.tiles[0] = ((plan.na + kBM - 1) / kBM) * tiles_n;
+    plan.tiles[1] = tiles_m * ((plan.nb + kBN - 1) / kBN);
+    plan.tiles[2] = plan.full ? tiles_m * tiles_n : 0;
+    return plan;
+}
+
+struct DecodeArgs {
+    const uint8_t* codes[2];   // A, B: [rows, K / 2]
+    const uint8_t* raw[2];     // raw UE5M3 scale atoms
+    const int* rec[2];
+    int rows[2];               // M, N
+    int K;
+    __nv_bfloat16* compact[2]; // [kRecMaxRows, K]
+    __nv_bfloat16* full[2];    // [rows, K]
+};
+
+// eight codes (one 32-bit word) x one scale -> eight bf16 values
+__device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
+    uint32_t out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = __fmul_rn(e2m1_value((word >> (8 * i)) & 0xFu), scale);
+        const float hi = __fmul_rn(e2m1_value((word >> (8 * i + 4)) & 0xFu), scale);
+        out[i] = float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+__device__ __forceinline__ void decode_rows(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ raw,
+                                            const int* __restrict__ list, int64_t nrows, int K,
+                                            __nv_bfloat16* __restrict__ out) {
+    const int64_t words_per_row = K / 8;
+    const int64_t k_atoms = K / 64;
+    const int64_t total = nrows * words_per_row;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t slot = idx / words_per_row, w = idx % words_per_row;
+        const int64_t row = list ? (int64_t)__ldg(list + slot) : slot;
+        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (K / 2)) + w);
+        const int64_t k = w * 8;
+        const uint8_t byte = __ldg(raw + ((row >> 7) * k_atoms + (k >> 6)) * 512 + (row & 31) * 16 +
+                                   ((row >> 5) & 3) * 4 + ((k >> 4) & 3));
+        *reinterpret_cast<uint4*>(out + slot * K + k) = decode_word(word, ue5m3_decode(byte));
+    }
+}
+
+__global__ void __launch_bounds__(256) decode_operands_kernel(const DecodeArgs a) {
+    const Plan plan = make_plan(a.rec[0], a.rec[1], a.rows[0], a.rows[1]);
+    if (plan.na > 0)
+        decode_rows(a.codes[0], a.raw[0], a.rec[0] + kRecHeader, plan.na, a.K, a.compact[0]);
+    if (plan.nb > 0)
+        decode_rows(a.codes[1], a.raw[1], a.rec[1] + kRecHeader, plan.nb, a.K, a.compact[1]);
+    if (plan.full || plan.nb > 0) decode_rows(a.codes[0], a.raw[0], nullptr, a.rows[0], a.K, a.full[0]);
+    if (plan.full || plan.na > 0) decode_rows(a.codes[1], a.raw[1], nullptr, a.rows[1], a.K, a.full[1]);
+}
+
+struct Params {
+    int M, N, K;
+    int snap;
+    const float* alpha;
+    const void* bias;
+    int bias_dtype;
+    void* out;
+    int out_dtype;
+    long long ldo;
+    int* status;
+    const int* rec_a;
+    const int* rec_b;
+};
+
+struct __align__(8) Barriers {
+    unsigned long long full[kStages];
+    unsigned long long empty[kStages];
+    unsigned long long tmem_full[2];
+    unsigned long long tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void fadd2_rz(float& c0, float& c1, uint32_t v0, uint32_t v1) {
+    asm("{\n"
+        ".reg .b64 a, b;\n"
+        "mov.b64 a, {%0, %1};\n"
+        "mov.b64 b, {%2, %3};\n"
+        "add.rz.f32x2 a, a, b;\n"
+        "mov.b64 {%0, %1}, a;\n"
+        "}\n"
+        : "+f"(c0), "+f"(c1)
+        : "r"(v0), "r"(v1));
+}
+
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// which product, which tile of it, and where its results go
+struct Tile {
+    int job;            // 0 row pass, 1 column pass, 2 full pass
+    int m0, n0;         // tile origin in the job's own row / column numbering
+    int rows, cols;     // extent of the job's output
+};
+
+__device__ __forceinline__ Tile locate_tile(const Plan& plan, int t, int M, int N) {
+    Tile tile;
+    const int tiles_n = (N + kBN - 1) / kBN;
+    if (t < plan.tiles[0]) {
+        tile.job = 0; tile.m0 = (t / tiles_n) * kBM; tile.n0 = (t % tiles_n) * kBN;
+        tile.rows = plan.na; tile.cols = N;
+        return tile;
+    }
+    t -= plan.tiles[0];
+    if (t < plan.tiles[1]) {
+        const int col_tiles = (plan.nb + kBN - 1) / kBN;
+        tile.job = 1; tile.m0 = (t / col_tiles) * kBM; tile.n0 = (t % col_tiles) * kBN;
+        tile.rows = M; tile.cols = plan.nb;
+        return tile;
+    }
+    t -= plan.tiles[1];
+    tile.job = 2; tile.m0 = (t / tiles_n) * kBM; tile.n0 = (t % tiles_n) * kBN;
+    tile.rows = M; tile.cols = N;
+    return tile;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT to_out(float v);
+template <>
+__device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// one thread's 128 finished values of one output row
+template <typename OutT>
+__device__ __forceinline__ void store_row(const Params& p, const Tile& tile, const float (&c)[kBN / 2],
+                                          long long out_row, int col0) {
+    OutT* out = static_cast<OutT*>(p.out) + out_row * p.ldo;
+    const int* col_map = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
+    constexpr int kVec = 16 / (int)sizeof(OutT);
+    const bool vec = !col_map && (p.ldo % kVec) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+    for (int i = 0; i < kBN / 2; i += kVec) {
+        if (vec && col0 + i + kVec <= tile.cols) {
+            OutT tmp[kVec];
+#pragma unroll
+            for (int e = 0; e < kVec; ++e) tmp[e] = to_out<OutT>(c[i + e]);
+            *reinterpret_cast<uint4*>(out + col0 + i) = *reinterpret_cast<const uint4*>(tmp);
+        } else {
+#pragma unroll
+            for (int e = 0; e < kVec; ++e) {
+                const int col = col0 + i + e;
+                if (col < tile.cols) out[col_map ? __ldg(col_map + col) : col] = to_out<OutT>(c[i + e]);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
+                     const __grid_constant__ CUtensorMap map_b_full,
+                     const __grid_constant__ CUtensorMap map_a_full,
+                     const __grid_constant__ CUtensorMap map_b_compact, const Params p) {
+    const Plan plan = make_plan(p.rec_a, p.rec_b, p.M, p.N);
+    const int total_tiles = plan.tiles[0] + plan.tiles[1] + plan.tiles[2];
+    if ((int)blockIdx.x >= total_tiles) return;  // the whole CTA, before anything is set up
+
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_issues = p.K / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->tmem_full[b], 1);
+            mbar_init(&bars->tmem_empty[b], kEpilogueWarps);
+        }
+        // a launch that follows a recorded failure does no work at all
+        bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&bars->tmem_base, kTmemCols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *((volatile uint32_t*)&bars->tmem_base);
+    const bool dead = *((volatile int*)&bars->abort_flag) != 0;
+
+    if (dead) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int g = 0;  // issues since the kernel started, over all tiles of this CTA
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const Tile tile = locate_tile(plan, t, p.M, p.N);
+                const CUtensorMap* ma = tile.job == 0 ? &map_a_compact : &map_a_full;
+                const CUtensorMap* mb = tile.job == 1 ? &map_b_compact : &map_b_full;
+                for (int j = 0; j < num_issues; ++j, ++g) {
+                    const int s = g % kStages;
+                    const uint32_t use = g / kStages;
+                    if (use > 0 && !mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* sa = smem + s * kStageBytes;
+                    unsigned char* sb = sa + kStageBytesA;
+                    mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
+                    tma_load_2d(sa, ma, &bars->full[s], j * kBK, tile.m0);
+                    tma_load_2d(sb, mb, &bars->full[s], j * kBK, tile.n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(kBM, kBN);
+            int g = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int j = 0; j < num_issues; ++j, ++g) {
+                    const int s = g % kStages;
+                    const int b = g & 1;
+                    const uint32_t use_b = g >> 1;
+                    if (use_b > 0 && !mbar_wait(&bars->tmem_empty[b], (use_b - 1) & 1, &bars->abort_flag, p.status, 12, g)) {
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&bars->full[s], (g / kStages) & 1, &bars->abort_flag, p.status, 13, g)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * kStageBytes);
+                    const uint64_t desc_a = smem_desc_sw128(sa);
+                    const uint64_t desc_b = smem_desc_sw128(sa + kStageBytesA);
+                    const uint32_t tmem_d = tmem_base + (uint32_t)b * kBN;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        umma_bf16(tmem_d, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc, k > 0 ? 1u : 0u);
+                    umma_commit(&bars->empty[s]);
+                    umma_commit(&bars->tmem_full[b]);
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;
+        const int h = (warp - 2) >> 2;
+        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        int g = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const Tile tile = locate_tile(plan, t, p.M, p.N);
+            float c[kBN / 2];
+#pragma unroll
+            for (int i = 0; i < kBN / 2; ++i) c[i] = 0.0f;
+            for (int j = 0; j < num_issues; ++j, ++g) {
+                const int b = g & 1;
+                ok = mbar_wait(&bars->tmem_full[b], (g >> 1) & 1, &bars->abort_flag, p.status, 14, g);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * (kBN / 2));
+#pragma unroll
+                for (int half = 0; half < kBN / 2 / 64; ++half) {
+                    uint32_t v0[32], v1[32];
+                    tmem_load_32_async(taddr + half * 64, v0);
+                    tmem_load_32_async(taddr + half * 64 + 32, v1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        fadd2_rz(c[half * 64 + i], c[half * 64 + i + 1], v0[i], v0[i + 1]);
+                        fadd2_rz(c[half * 64 + 32 + i], c[half * 64 + 33 + i], v1[i], v1[i + 1]);
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+            }
+            if (!ok) break;
+            const int local_row = tile.m0 + q * 32 + lane;
+            if (local_row >= tile.rows) continue;
+            const long long out_row = tile.job == 0 ? (long long)__ldg(p.rec_a + kRecHeader + local_row) : local_row;
+            const int col0 = tile.n0 + h * (kBN / 2);
+            const int* col_map = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
+#pragma unroll
+            for (int i = 0; i < kBN / 2; ++i) {
+                float v = c[i];
+                if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
+                if (p.alpha) v = __fmul_rn(v, alpha);
+                c[i] = v;
+            }
+            if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < kBN / 2; ++i) {
+                    const int col = col0 + i;
+                    if (col < tile.cols) {
+                        const int out_col = col_map ? __ldg(col_map + col) : col;
+                        const float bv = p.bias_dtype == UE5M3_DTYPE_BF16
+                                             ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[out_col])
+                                             : static_cast<const float*>(p.bias)[out_col];
+                        c[i] = __fadd_rn(c[i], bv);
+                    }
+                }
+            }
+            if (p.out_dtype == UE5M3_DTYPE_BF16) store_row<__nv_bfloat16>(p, tile, c, out_row, col0);
+            else store_row<float>(p, tile, c, out_row, col0);
+        }
+    }
+
+    // common exit: every role's loop is bounded, so all threads arrive here
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
+            query != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+// [rows, K] bf16 row-major -> 2-D tiled map with a (64 x box_rows) box, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, uint32_t box_rows) {
+    PFN_cuTensorMapEncodeTiled_v12000 encode = encode_fn();
+    if (!encode) {
+        record_error_text("cuTensorMapEncodeTiled is not available from the driver");
+        return UE5M3_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        record_error_text("cuTensorMapEncodeTiled failed for a decoded operand");
+        return UE5M3_ERR_CUDA;
+    }
+    return UE5M3_OK;
+}
+
+}  // namespace fb
+}  // namespace ue5m3
+
+using namespace ue5m3;
+
+extern "C" size_t ue5m3_gemm_fp4_fallback_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return (size_t)(M + N + 2 * (int64_t)kRecMaxRows) * (size_t)K * 2;
+}
+
+extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_sf_raw, const int* a_record,
+                                       const uint8_t* b_codes, const uint8_t* b_sf_raw, const int* b_record,
+                                       int64_t M, int64_t N, int64_t K, int snap, const float* alpha_dev,
+                                       const void* bias, int bias_dtype, void* out, int out_dtype, int64_t ldo,
+                                       void* workspace, size_t workspace_bytes, int* status_dev, void* stream_v) {
+    if (!a_codes || !a_sf_raw || !a_record || !b_codes || !b_sf_raw || !b_record || !out || !workspace ||
+        M <= 0 || N <= 0 || K <= 0)
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (K % fb::kBK) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if (out_dtype != UE5M3_DTYPE_BF16 && out_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (bias && bias_dtype != UE5M3_DTYPE_BF16 && bias_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (ldo < N) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    if (((M + 127) / 128) * ((N + 255) / 256) > 0x3FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    if (((uintptr_t)workspace % 16) || ((uintptr_t)a_codes % 4) || ((uintptr_t)b_codes % 4) || (K / 2) % 4)
+        return UE5M3_ERR_ALIGNMENT;
+    if (workspace_bytes < ue5m3_gemm_fp4_fallback_workspace_bytes(M, N, K)) return UE5M3_ERR_SCRATCH;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    __nv_bfloat16* ws = static_cast<__nv_bfloat16*>(workspace);
+    fb::DecodeArgs d;
+    d.codes[0] = a_codes; d.codes[1] = b_codes;
+    d.raw[0] = a_sf_raw; d.raw[1] = b_sf_raw;
+    d.rec[0] = a_record; d.rec[1] = b_record;
+    d.rows[0] = (int)M; d.rows[1] = (int)N; d.K = (int)K;
+    d.compact[0] = ws;
+    d.compact[1] = d.compact[0] + (size_t)kRecMaxRows * K;
+    d.full[0] = d.compact[1] + (size_t)kRecMaxRows * K;
+    d.full[1] = d.full[0] + (size_t)M * K;
+    fb::decode_operands_kernel<<<sm_count() * 8, 256, 0, stream>>>(d);
+    int status = check_launch();
+    if (status != UE5M3_OK) return status;
+
+    CUtensorMap map_ac, map_bf, map_af, map_bc;
+    if ((status = fb::make_map(&map_ac, d.compact[0], kRecMaxRows, K, fb::kBM)) != UE5M3_OK) return status;
+    if ((status = fb::make_map(&map_bf, d.full[1], N, K, fb::kBN)) != UE5M3_OK) return status;
+    if ((status = fb::make_map(&map_af, d.full[0], M, K, fb::kBM)) != UE5M3_OK) return status;
+    if ((status = fb::make_map(&map_bc, d.compact[1], kRecMaxRows, K, fb::kBN)) != UE5M3_OK) return status;
+
+    fb::Params p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
+    p.alpha = alpha_dev; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
+    p.rec_a = a_record; p.rec_b = b_record;
+    const size_t smem = (size_t)fb::kStages * fb::kStageBytes + sizeof(fb::Barriers) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(fb::gemm_fallback_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    fb::gemm_fallback_kernel<<<sm_count(), fb::kThreads, smem, stream>>>(map_ac, map_bf, map_af, map_bc, p);
+    return check_launch();
+}

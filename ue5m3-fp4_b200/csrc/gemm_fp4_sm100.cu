@@ -28,6 +28,7 @@
 
 #include "abi_common.cuh"
 #include "tcgen05_ptx.cuh"
+#include "window_record.cuh"
 
 namespace ue5m3 {
 
@@ -752,15 +753,16 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // Source scales are [rows/row_group][K/block] bytes (row_group = 1 for 1-D blocks, = block
 // for 2-D tiles); a 32-wide block feeds two consecutive 16-blocks.
 // byte_out = byte_in - ((8 + shift) << 3): same fraction bits, exponent re-biased from 15 to
-// 7 and divided by 2^shift.  Valid UE4M3 exponents are 1..15 (and not 0x7F); anything else
-// raises *window_flag.  Rows beyond `rows` get 1.0 (0x38).
+// 7 and divided by 2^shift.  Valid UE4M3 exponents are 1..15 (and not 0x7F); anything else is
+// clamped and its row goes into the window record.  Rows beyond `rows` get 1.0 (0x38).
 // ---------------------------------------------------------------------------------------
 __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales, int64_t rows, int64_t kblocks,
                                    int block, int row_group, int shift, uint32_t* __restrict__ out,
-                                   int64_t row_tiles, int64_t k_atoms, int* __restrict__ window_flag) {
+                                   uint32_t* __restrict__ out_raw, int64_t row_tiles, int64_t k_atoms,
+                                   int* __restrict__ window_record) {
     const int64_t total = row_tiles * k_atoms * 128;
     const int per16 = block / 16;
-    bool bad = false;
+    int bad_units = 0;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int word = (int)(i % 128);           // r0 * 4 + r1
@@ -768,25 +770,27 @@ __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales, int64_t r
         const int64_t ka = atom % k_atoms, tile = atom / k_atoms;
         const int r0 = word >> 2, r1 = word & 3;
         const int64_t row = tile * 128 + r1 * 32 + r0;
-        uint32_t packed = 0x38383838u;
+        uint32_t packed = 0x38383838u, raw = 0x78787878u;
         if (row < rows) {
-            packed = 0u;
+            packed = raw = 0u;
             const uint8_t* src = scales + (row / row_group) * kblocks;
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) {
                 const int64_t h = ka * 4 + kb;     // 16-wide block index along K
-                int code5 = src[h / per16];
-                int code4 = code5 - ((8 + shift) << 3);
-                if (code4 < 8 || code4 > 0x7E) {
-                    bad = true;
-                    code4 = code4 < 8 ? 8 : 0x7E;
+                const uint32_t code5 = src[h / per16];
+                bool outside;
+                packed |= ue4m3_window_byte(code5, (8 + shift) << 3, outside) << (8 * kb);
+                raw |= code5 << (8 * kb);
+                if (outside) {
+                    ++bad_units;
+                    window_record_row(window_record, row);
                 }
-                packed |= (uint32_t)code4 << (8 * kb);
             }
         }
         out[atom * 128 + word] = packed;
+        if (out_raw) out_raw[atom * 128 + word] = raw;
     }
-    if (bad) atomicExch(window_flag, 1);
+    window_record_units(window_record, bad_units);
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 fp4_encode_fn() {
@@ -858,26 +862,31 @@ static bool use_cta_pair(int64_t M) {
 
 using namespace ue5m3;
 
+extern "C" size_t ue5m3_window_record_ints(int64_t operand_rows) {
+    if (operand_rows <= 0) return 0;
+    return (size_t)kRecHeader + (size_t)kRecMaxRows + (size_t)operand_rows;
+}
+
 extern "C" size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K) {
     if (rows <= 0 || K <= 0 || K % 64) return 0;
     return (size_t)((rows + 127) / 128) * (size_t)(K / 64) * kSfAtomBytes;
 }
 
 extern "C" int ue5m3_pack_scales_ue4m3(const uint8_t* scales, int64_t rows, int64_t K, int block,
-                                       int two_d, int shift, uint8_t* sf_out, int* window_flag,
-                                       void* stream_v) {
-    if (!scales || !sf_out || !window_flag || rows <= 0 || K <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+                                       int two_d, int shift, uint8_t* sf_out, uint8_t* sf_raw,
+                                       int* window_record, void* stream_v) {
+    if (!scales || !sf_out || !window_record || rows <= 0 || K <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (block != 16 && block != 32) return UE5M3_ERR_BLOCK_SIZE;
     if (K % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if (shift < -8 || shift > 8) return UE5M3_ERR_INVALID_ARGUMENT;
-    if (((uintptr_t)sf_out % 16) != 0) return UE5M3_ERR_ALIGNMENT;
+    if (((uintptr_t)sf_out % 16) != 0 || ((uintptr_t)sf_raw % 16) != 0) return UE5M3_ERR_ALIGNMENT;
     const int64_t row_tiles = (rows + 127) / 128, k_atoms = K / 64;
     const int64_t total = row_tiles * k_atoms * 128;
     int64_t want = (total + 255) / 256;
     int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
     pack_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
         scales, rows, K / block, block, two_d ? block : 1, shift, reinterpret_cast<uint32_t*>(sf_out),
-        row_tiles, k_atoms, window_flag);
+        reinterpret_cast<uint32_t*>(sf_raw), row_tiles, k_atoms, window_record);
     return check_launch();
 }
 

@@ -18,6 +18,7 @@
 #include <stdint.h>
 
 #include "quantize_common.cuh"
+#include "window_record.cuh"
 
 namespace ue5m3 {
 
@@ -191,6 +192,7 @@ struct TileSmem {
     __align__(16) uint8_t stage_n[kTileRows][kTileCols / 2];  // codes  : [row][col/2]
     __align__(8) uint8_t scale_t[kTileCols][8];               // COL scales_t: [col][row group]
     __align__(8) uint8_t sf_t[kTileCols][8];                  // UE4M3 bytes per 16 rows of the tile
+    __align__(8) uint8_t sf_raw_t[kTileCols][8];              // the same blocks' UE5M3 bytes
 };
 
 struct TileArgs {
@@ -210,8 +212,9 @@ struct TileArgs {
     int vec_ok;  // x (and bits) rows start on 16-byte boundaries
     // transposed operand of the FP4 GEMM: scale atoms [ceil(cols/128)][rows/64][128 words]
     uint32_t* sf_t;
+    uint32_t* sf_raw_t;  // same layout, unmodified UE5M3 bytes, may be null
     int shift;
-    int* window_flag;
+    int* window_record;  // see include/ue5m3_fp4.h
 };
 
 template <typename T, int B, bool TWO_D, int RMODE, int BITS>
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
     const int64_t nbr = (a.rows + B - 1) / B;  // scale rows
     const int64_t nbc = (a.cols + B - 1) / B;  // scale columns (2D)
     const bool want_fake = a.fake != nullptr || a.fake_t != nullptr;
-    bool bad = false;
+    int bad_units = 0;
 #pragma unroll 1
     for (int item = tid; item < kItems; item += 256) {
         const int c = item % kTileCols;
@@ -295,13 +298,17 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
         const float rcp = payload_multiplier(scale, ts);
         const float sd = __fmul_rn(scale, ts.dec);
         if (a.sf_t) {
-            int code4 = (int)code - ((8 + a.shift) << 3);
-            if (code4 < 8 || code4 > 0x7E) {
-                if (c0 + c < a.cols && r0 + (int64_t)g * B < a.rows) bad = true;
-                code4 = code4 < 8 ? 8 : 0x7E;
+            bool outside;
+            const uint32_t code4 = ue4m3_window_byte(code, (8 + a.shift) << 3, outside);
+            if (outside && c0 + c < a.cols && r0 + (int64_t)g * B < a.rows) {
+                bad_units += B / 16;
+                window_record_row(a.window_record, c0 + c);
             }
 #pragma unroll
-            for (int h = 0; h < B / 16; ++h) s.sf_t[c][g * (B / 16) + h] = (uint8_t)code4;
+            for (int h = 0; h < B / 16; ++h) {
+                s.sf_t[c][g * (B / 16) + h] = (uint8_t)code4;
+                s.sf_raw_t[c][g * (B / 16) + h] = (uint8_t)code;
+            }
         }
         uint32_t nib[B];
         if (RMODE == kRoundTteHw) {
@@ -396,7 +403,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
     }
     if (a.sf_t) {
         // 64 operand rows (tile columns) x two K atoms (tile rows 0..63, 64..127): one word each
-        if (bad) atomicExch(a.window_flag, 1);
+        window_record_units(a.window_record, bad_units);
         const int64_t k_atoms = a.rows / 64;
         if (tid < 2 * kTileCols) {
             const int c = tid >> 1, half = tid & 1;
@@ -404,12 +411,17 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
             const int64_t ka = r0 / 64 + half;
             if (ka < k_atoms) {
                 uint32_t word = *reinterpret_cast<const uint32_t*>(&s.sf_t[c][4 * half]);
-                if (orow >= a.cols) word = 0x38383838u;
-                a.sf_t[((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)] = word;
+                uint32_t raw_word = *reinterpret_cast<const uint32_t*>(&s.sf_raw_t[c][4 * half]);
+                if (orow >= a.cols) { word = 0x38383838u; raw_word = 0x78787878u; }
+                const int64_t at = ((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3);
+                a.sf_t[at] = word;
+                if (a.sf_raw_t) a.sf_raw_t[at] = raw_word;
                 // the last column tile also pads the rest of its 128-row atom
                 if (c0 + kTileCols >= a.cols && ((c0 + kTileCols) & 127) != 0) {
                     const int64_t prow = orow + kTileCols;
-                    a.sf_t[((prow >> 7) * k_atoms + ka) * 128 + (prow & 31) * 4 + ((prow >> 5) & 3)] = 0x38383838u;
+                    const int64_t pat = ((prow >> 7) * k_atoms + ka) * 128 + (prow & 31) * 4 + ((prow >> 5) & 3);
+                    a.sf_t[pat] = 0x38383838u;
+                    if (a.sf_raw_t) a.sf_raw_t[pat] = 0x78787878u;
                 }
             }
         }
@@ -593,16 +605,16 @@ using namespace ue5m3;
 namespace ue5m3 {
 int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
                             const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
-                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, bool rht,
-                            cudaStream_t stream);
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, uint8_t* sf_raw_t, int* window_record,
+                            bool rht, cudaStream_t stream);
 }
 
 static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t cols, int block,
                              int blocking, const float* amax_dev, float target, int rounding,
                              const void* bits, int bits_dtype, uint8_t* codes, uint8_t* scales,
                              uint8_t* codes_t, uint8_t* scales_t, void* fake, void* fake_t,
-                             int fake_dtype, int fake_domain, uint32_t* sf_t, int shift,
-                             int* window_flag, void* stream_v) {
+                             int fake_dtype, int fake_domain, uint32_t* sf_t, uint32_t* sf_raw_t, int shift,
+                             int* window_record, void* stream_v) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (!x || !amax_dev || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
@@ -664,7 +676,7 @@ static int quantize_dispatch(const void* x, int dtype, int64_t rows, int64_t col
     args.bits = bits; args.codes = codes; args.scales = scales; args.codes_t = codes_t;
     args.scales_t = scales_t; args.fake = fake; args.fake_t = fake_t; args.fake_dtype = fake_dtype;
     args.fake_domain = fake_domain;
-    args.sf_t = sf_t; args.shift = shift; args.window_flag = window_flag;
+    args.sf_t = sf_t; args.sf_raw_t = sf_raw_t; args.shift = shift; args.window_record = window_record;
     const bool fake_vec = !fake || (((uintptr_t)fake % 16) == 0 && (cols * fsize) % 16 == 0);
     const bool fake_t_ok = !fake_t || ((uintptr_t)fake_t % 16) == 0;
     if (!fake_t_ok) return UE5M3_ERR_ALIGNMENT;
@@ -689,18 +701,18 @@ extern "C" int ue5m3_quantize(const void* x, int dtype, int64_t rows, int64_t co
                               int fake_dtype, int fake_domain, void* stream_v) {
     return quantize_dispatch(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
                              bits_dtype, codes, scales, codes_t, scales_t, fake, fake_t, fake_dtype,
-                             fake_domain, nullptr, 0, nullptr, stream_v);
+                             fake_domain, nullptr, nullptr, 0, nullptr, stream_v);
 }
 
 extern "C" int ue5m3_quantize_fp4_operand_t(const void* x, int dtype, int64_t rows, int64_t cols,
                                             int block, int blocking, const float* amax_dev,
                                             float target, int rounding, const void* bits,
                                             int bits_dtype, int shift, uint8_t* codes_t, uint8_t* sf_t,
-                                            int* window_flag, void* stream_v) {
-    if (!codes_t || !sf_t || !window_flag || shift < -8 || shift > 16) return UE5M3_ERR_INVALID_ARGUMENT;
+                                            uint8_t* sf_raw_t, int* window_record, void* stream_v) {
+    if (!codes_t || !sf_t || !window_record || shift < -8 || shift > 16) return UE5M3_ERR_INVALID_ARGUMENT;
     if (blocking != UE5M3_BLOCK_COL && blocking != UE5M3_BLOCK_2D) return UE5M3_ERR_UNSUPPORTED;
     if (rows % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
-    if ((uintptr_t)sf_t % 16) return UE5M3_ERR_ALIGNMENT;
+    if (((uintptr_t)sf_t % 16) || ((uintptr_t)sf_raw_t % 16)) return UE5M3_ERR_ALIGNMENT;
     if (!x || !amax_dev || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (block != 16 && block != 32) return UE5M3_ERR_BLOCK_SIZE;
@@ -714,14 +726,14 @@ extern "C" int ue5m3_quantize_fp4_operand_t(const void* x, int dtype, int64_t ro
     const char* general = getenv("UE5M3_TRANSPOSE_KERNEL");
     if (!(general && general[0] == '0')) {
         int fast = quantize_operand_t_fast(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
-                                           bits_dtype, shift, codes_t, sf_t, window_flag, false,
+                                           bits_dtype, shift, codes_t, sf_t, sf_raw_t, window_record, false,
                                            static_cast<cudaStream_t>(stream_v));
         if (fast != UE5M3_ERR_UNSUPPORTED) return fast;
     }
     return quantize_dispatch(x, dtype, rows, cols, block, blocking, amax_dev, target, rounding, bits,
                              bits_dtype, nullptr, nullptr, codes_t, nullptr, nullptr, nullptr,
-                             UE5M3_DTYPE_BF16, UE5M3_FAKE_NONE, reinterpret_cast<uint32_t*>(sf_t), shift,
-                             window_flag, stream_v);
+                             UE5M3_DTYPE_BF16, UE5M3_FAKE_NONE, reinterpret_cast<uint32_t*>(sf_t),
+                             reinterpret_cast<uint32_t*>(sf_raw_t), shift, window_record, stream_v);
 }
 
 extern "C" int ue5m3_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t rows,

@@ -12,6 +12,7 @@
 // Numerics: ue5m3_device.cuh (formats.py:350-457 of the reference).  The UE4M3 re-bias has no
 // counterpart in the reference; it is exact inside the window and flagged outside.
 #include "quantize_common.cuh"
+#include "window_record.cuh"
 
 namespace ue5m3 {
 
@@ -23,9 +24,10 @@ struct OperandArgs {
     const void* bits;
     uint8_t* codes;     // [rows, cols / 2]
     uint32_t* sf;       // [ceil(rows / 128)][cols / 64][128] words, may be null
+    uint32_t* sf_raw;   // same layout, unmodified UE5M3 bytes, may be null
     uint8_t* scales;    // raw UE5M3 bytes ([rows, cols/B] or [ceil(rows/B), cols/B]), may be null
     int shift;
-    int* window_flag;
+    int* window_record; // see include/ue5m3_fp4.h
 };
 
 // U = 16-element units per lane and task: 4 (one whole atom row, 128 input bytes per lane) or
@@ -44,7 +46,7 @@ quantize_operand_kernel(const OperandArgs a) {
     const int64_t ntasks = row_groups * k_tasks;
     const int64_t nbc = a.cols / B;
     const int rebias = (8 + a.shift) << 3;
-    bool bad = false;
+    int bad_units = 0;
 
     for (int64_t task = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); task < ntasks;
          task += (int64_t)gridDim.x * 8) {
@@ -98,7 +100,7 @@ quantize_operand_kernel(const OperandArgs a) {
         }
 
         uint32_t code[U];
-        uint32_t sf_bytes = 0u;
+        uint32_t sf_bytes = 0u, raw_bytes = 0u;
         uint32_t packed[U][2];
         float scale = 1.0f;
 #pragma unroll
@@ -108,12 +110,13 @@ quantize_operand_kernel(const OperandArgs a) {
             } else {
                 block_scale_converged(m[u], ts, code[u], scale);
             }
-            int code4 = (int)code[u] - rebias;
-            if (code4 < 8 || code4 > 0x7E) {
-                bad = bad || valid;
-                code4 = code4 < 8 ? 8 : 0x7E;
+            bool outside;
+            sf_bytes |= ue4m3_window_byte(code[u], rebias, outside) << (8 * u);
+            raw_bytes |= code[u] << (8 * u);
+            if (outside && valid && a.sf) {
+                ++bad_units;
+                window_record_row(a.window_record, row);
             }
-            sf_bytes |= (uint32_t)code4 << (8 * u);
             const float rcp = payload_multiplier(scale, ts);
             float v[16];
             unit_values(raw[u], v);
@@ -179,15 +182,19 @@ quantize_operand_kernel(const OperandArgs a) {
             const int r1 = (int)(rg & 3);
             const int64_t ka = col0 / 64;
             uint32_t* word = a.sf + (tile * k_atoms + ka) * 128 + lane * 4 + r1;
+            uint32_t* raw_word = a.sf_raw ? a.sf_raw + (word - a.sf) : nullptr;
             if (U == 4) {
                 *word = valid ? sf_bytes : 0x38383838u;
+                if (raw_word) *raw_word = valid ? raw_bytes : 0x78787878u;
             } else {
-                uint16_t* half = reinterpret_cast<uint16_t*>(word) + (col0 % 64) / 32;
-                *half = valid ? (uint16_t)sf_bytes : (uint16_t)0x3838u;
+                const int half_index = (int)((col0 % 64) / 32);
+                reinterpret_cast<uint16_t*>(word)[half_index] = valid ? (uint16_t)sf_bytes : (uint16_t)0x3838u;
+                if (raw_word)
+                    reinterpret_cast<uint16_t*>(raw_word)[half_index] = valid ? (uint16_t)raw_bytes : (uint16_t)0x7878u;
             }
         }
     }
-    if (bad && a.window_flag) atomicExch(a.window_flag, 1);
+    if (a.sf) window_record_units(a.window_record, bad_units);
 }
 
 template <typename T, int B, bool TWO_D>
@@ -243,8 +250,9 @@ struct OperandTArgs {
     const void* bits;
     uint8_t* codes_t;     // [cols, rows / 2]
     uint8_t* sf_t;        // atoms of the [cols, rows] operand
+    uint8_t* sf_raw_t;    // same layout, unmodified UE5M3 bytes, may be null
     int shift;
-    int* window_flag;
+    int* window_record;   // see include/ue5m3_fp4.h
     unsigned int* transformed_amax;  // amax-only mode: max |transformed value| as fp32 bits
 };
 
@@ -389,9 +397,9 @@ quantize_operand_t_kernel(const OperandTArgs a) {
     }
 
     const int rebias = (8 + a.shift) << 3;
-    bool bad = false;
+    int bad_units = 0;
     uint32_t packed[2][4];   // [column][32 rows = 4 words]
-    uint32_t sf_pair[2] = {0u, 0u};
+    uint32_t sf_pair[2] = {0u, 0u}, raw_pair[2] = {0u, 0u};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         float u[2][16];
@@ -432,12 +440,13 @@ quantize_operand_t_kernel(const OperandTArgs a) {
             uint32_t code;
             float scale;
             block_scale_converged(m[h][j], ts, code, scale);
-            int code4 = (int)code - rebias;
-            if (code4 < 8 || code4 > 0x7E) {
-                bad = bad || (rows_valid && col + j < a.cols);
-                code4 = code4 < 8 ? 8 : 0x7E;
+            bool outside;
+            sf_pair[j] |= ue4m3_window_byte(code, rebias, outside) << (8 * h);
+            raw_pair[j] |= code << (8 * h);
+            if (outside && rows_valid && col + j < a.cols) {
+                ++bad_units;
+                window_record_row(a.window_record, col + j);
             }
-            sf_pair[j] |= (uint32_t)code4 << (8 * h);
             const float rcp = payload_multiplier(scale, ts);
 #pragma unroll
             for (int i = 0; i < 16; i += 2) mul2_rn(u[j][i], u[j][i + 1], rcp);
@@ -475,11 +484,13 @@ quantize_operand_t_kernel(const OperandTArgs a) {
                 *reinterpret_cast<uint4*>(a.codes_t + orow * (a.rows / 2) + krow / 2) =
                     make_uint4(packed[j][0], packed[j][1], packed[j][2], packed[j][3]);
             // the tile spans one whole 128-row group of the operand: rows beyond `cols` get 1.0
-            uint8_t* word_ptr = a.sf_t + (((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)) * 4;
-            *reinterpret_cast<uint16_t*>(word_ptr + kb0) = orow < a.cols ? (uint16_t)sf_pair[j] : (uint16_t)0x3838u;
+            const int64_t byte_offset = (((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)) * 4 + kb0;
+            *reinterpret_cast<uint16_t*>(a.sf_t + byte_offset) = orow < a.cols ? (uint16_t)sf_pair[j] : (uint16_t)0x3838u;
+            if (a.sf_raw_t)
+                *reinterpret_cast<uint16_t*>(a.sf_raw_t + byte_offset) = orow < a.cols ? (uint16_t)raw_pair[j] : (uint16_t)0x7878u;
         }
     }
-    if (bad) atomicExch(a.window_flag, 1);
+    window_record_units(a.window_record, bad_units);
 }
 
 template <typename T, int B, bool TWO_D, bool RHT>
@@ -510,8 +521,8 @@ static int dispatch_operand_t(int rmode, int bits_dtype, const OperandTArgs& arg
 // caller should use that one.
 int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols, int block, int blocking,
                             const float* amax_dev, float target, int rounding, const void* bits, int bits_dtype,
-                            int shift, uint8_t* codes_t, uint8_t* sf_t, int* window_flag, bool rht,
-                            cudaStream_t stream) {
+                            int shift, uint8_t* codes_t, uint8_t* sf_t, uint8_t* sf_raw_t, int* window_record,
+                            bool rht, cudaStream_t stream) {
     const bool sr = rounding == UE5M3_ROUND_STOCHASTIC_FAST;
     const size_t esize = dtype == UE5M3_DTYPE_BF16 ? 2 : 4;
     if (((uintptr_t)x % 16) || (cols * esize) % 16 || ((uintptr_t)codes_t % 16) || (rows % 64)) return UE5M3_ERR_UNSUPPORTED;
@@ -522,7 +533,8 @@ int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols
     OperandTArgs args;
     args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;
     args.six_t = (float)((double)target * 6.0);
-    args.bits = bits; args.codes_t = codes_t; args.sf_t = sf_t; args.shift = shift; args.window_flag = window_flag;
+    args.bits = bits; args.codes_t = codes_t; args.sf_t = sf_t; args.sf_raw_t = sf_raw_t; args.shift = shift;
+    args.window_record = window_record;
     args.transformed_amax = nullptr;
     const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
     const bool two_d = blocking == UE5M3_BLOCK_2D;
@@ -551,7 +563,8 @@ extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows
                                           int block, int blocking, const float* amax_dev,
                                           float target, int rounding, const void* bits,
                                           int bits_dtype, int shift, uint8_t* codes, uint8_t* sf,
-                                          uint8_t* scales, int* window_flag, void* stream_v) {
+                                          uint8_t* sf_raw, uint8_t* scales, int* window_record,
+                                          void* stream_v) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (!x || !amax_dev || !codes || rows <= 0 || cols <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
@@ -564,9 +577,11 @@ extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows
                          bits_dtype != UE5M3_BITS_PHILOX)))
         return UE5M3_ERR_INVALID_ARGUMENT;
     if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
-    if (sf && (!window_flag || shift < -8 || shift > 16)) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (sf && (!window_record || shift < -8 || shift > 16)) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (sf_raw && !sf) return UE5M3_ERR_INVALID_ARGUMENT;
     if (cols % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
-    if (((uintptr_t)x % 32) || ((uintptr_t)codes % 16) || ((uintptr_t)sf % 16) || ((uintptr_t)scales % 4))
+    if (((uintptr_t)x % 32) || ((uintptr_t)codes % 16) || ((uintptr_t)sf % 16) || ((uintptr_t)sf_raw % 16) ||
+        ((uintptr_t)scales % 4))
         return UE5M3_ERR_ALIGNMENT;
     if (sr && ((uintptr_t)bits % (bits_dtype == UE5M3_BITS_PHILOX ? 8 : bits_dtype == UE5M3_BITS_U8 ? 16 : 32)))
         return UE5M3_ERR_ALIGNMENT;
@@ -575,7 +590,8 @@ extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows
     args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;
     args.six_t = (float)((double)target * 6.0);
     args.bits = bits; args.codes = codes; args.sf = reinterpret_cast<uint32_t*>(sf);
-    args.scales = scales; args.shift = shift; args.window_flag = window_flag;
+    args.sf_raw = reinterpret_cast<uint32_t*>(sf_raw);
+    args.scales = scales; args.shift = shift; args.window_record = window_record;
     const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
     const bool two_d = blocking == UE5M3_BLOCK_2D;
 #define UE5M3_DO(T, B) \
@@ -619,8 +635,9 @@ extern "C" int ue5m3_rht_amax_t(const void* x, int dtype, int64_t rows, int64_t 
 extern "C" int ue5m3_quantize_fp4_operand_t_rht(const void* x, int dtype, int64_t rows, int64_t cols,
                                                 const float* amax_dev, float target, int rounding,
                                                 const void* bits, int bits_dtype, int shift, uint8_t* codes_t,
-                                                uint8_t* sf_t, int* window_flag, void* stream_v) {
-    if (!x || !amax_dev || !codes_t || !sf_t || !window_flag || rows <= 0 || cols <= 0 || shift < -8 || shift > 16)
+                                                uint8_t* sf_t, uint8_t* sf_raw_t, int* window_record,
+                                                void* stream_v) {
+    if (!x || !amax_dev || !codes_t || !sf_t || !window_record || rows <= 0 || cols <= 0 || shift < -8 || shift > 16)
         return UE5M3_ERR_INVALID_ARGUMENT;
     if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (!(target > 0.0f) || !(target < 3.0e38f)) return UE5M3_ERR_INVALID_ARGUMENT;
@@ -629,9 +646,9 @@ extern "C" int ue5m3_quantize_fp4_operand_t_rht(const void* x, int dtype, int64_
     if (sr && (!bits || (bits_dtype != UE5M3_BITS_U8 && bits_dtype != UE5M3_BITS_PHILOX))) return UE5M3_ERR_INVALID_ARGUMENT;
     if (!sr && bits) return UE5M3_ERR_INVALID_ARGUMENT;
     if (rows % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
-    if ((uintptr_t)sf_t % 16) return UE5M3_ERR_ALIGNMENT;
+    if (((uintptr_t)sf_t % 16) || ((uintptr_t)sf_raw_t % 16)) return UE5M3_ERR_ALIGNMENT;
     int status = quantize_operand_t_fast(x, dtype, rows, cols, 16, UE5M3_BLOCK_COL, amax_dev, target, rounding, bits,
-                                         bits_dtype, shift, codes_t, sf_t, window_flag, true,
+                                         bits_dtype, shift, codes_t, sf_t, sf_raw_t, window_record, true,
                                          static_cast<cudaStream_t>(stream_v));
     return status == UE5M3_ERR_UNSUPPORTED ? UE5M3_ERR_ALIGNMENT : status;
 }

@@ -1,0 +1,39 @@
+// Device side of an operand's window record (layout: include/ue5m3_fp4.h).  The quantizers
+// call these on the rare block whose UE5M3 scale does not fit the tensor core's UE4M3 range.
+#pragma once
+
+#include <stdint.h>
+
+#include "abi_common.cuh"
+
+namespace ue5m3 {
+
+constexpr int kRecHeader = UE5M3_WINDOW_RECORD_HEADER;
+constexpr int kRecMaxRows = UE5M3_FALLBACK_MAX_ROWS;
+
+// Lists `row` once.  The plain read keeps rows with many such blocks off the atomic path.
+__device__ __forceinline__ void window_record_row(int* rec, int64_t row) {
+    int* flag = rec + kRecHeader + kRecMaxRows + row;
+    if (*((volatile int*)flag) == 0 && atomicExch(flag, 1) == 0) {
+        const int slot = atomicAdd(rec, 1);
+        if (slot < kRecMaxRows) rec[kRecHeader + slot] = (int)row;
+    }
+}
+
+// Adds a thread's count of out-of-window 16-element units, one atomic per warp at most.
+__device__ __forceinline__ void window_record_units(int* rec, int units) {
+    if (!__any_sync(0xFFFFFFFFu, units != 0)) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) units += __shfl_xor_sync(0xFFFFFFFFu, units, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(rec + 1, units);
+}
+
+// UE5M3 byte -> UE4M3 byte at `rebias` = (8 + shift) << 3; `outside` reports a clamp.
+__device__ __forceinline__ uint32_t ue4m3_window_byte(uint32_t code5, int rebias, bool& outside) {
+    int code4 = (int)code5 - rebias;
+    outside = code4 < 8 || code4 > 0x7E;
+    if (outside) code4 = code4 < 8 ? 8 : 0x7E;
+    return (uint32_t)code4;
+}
+
+}  // namespace ue5m3

@@ -75,15 +75,21 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_packed_scales_bytes.restype = sz
     lib.ue5m3_packed_scales_bytes.argtypes = [i64, i64]
     lib.ue5m3_pack_scales_ue4m3.restype = i32
-    lib.ue5m3_pack_scales_ue4m3.argtypes = [p, i64, i64, i32, i32, i32, p, p, p]
+    lib.ue5m3_pack_scales_ue4m3.argtypes = [p, i64, i64, i32, i32, i32, p, p, p, p]
+    lib.ue5m3_window_record_ints.restype = sz
+    lib.ue5m3_window_record_ints.argtypes = [i64]
     lib.ue5m3_quantize_fp4_operand.restype = i32
-    lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
+    lib.ue5m3_quantize_fp4_operand.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p, p]
     lib.ue5m3_quantize_fp4_operand_t.restype = i32
-    lib.ue5m3_quantize_fp4_operand_t.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p]
+    lib.ue5m3_quantize_fp4_operand_t.argtypes = [p, i32, i64, i64, i32, i32, p, f32, i32, p, i32, i32, p, p, p, p, p]
     lib.ue5m3_rht_amax_t.restype = i32
     lib.ue5m3_rht_amax_t.argtypes = [p, i32, i64, i64, p, p]
     lib.ue5m3_quantize_fp4_operand_t_rht.restype = i32
-    lib.ue5m3_quantize_fp4_operand_t_rht.argtypes = [p, i32, i64, i64, p, f32, i32, p, i32, i32, p, p, p, p]
+    lib.ue5m3_quantize_fp4_operand_t_rht.argtypes = [p, i32, i64, i64, p, f32, i32, p, i32, i32, p, p, p, p, p]
+    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.restype = sz
+    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.ue5m3_gemm_fp4_fallback.restype = i32
+    lib.ue5m3_gemm_fp4_fallback.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, p, p, i32, p, i32, i64, p, sz, p, p]
     lib.ue5m3_philox_bytes.restype = i32
     lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
@@ -93,7 +99,7 @@ def load() -> ctypes.CDLL:
     if hasattr(lib, "ue5m3_amax_static"):
         lib.ue5m3_amax_static.restype = i32
         lib.ue5m3_amax_static.argtypes = [p, i32, i64, p, p]
-    if lib.ue5m3_abi_version() != 1:
+    if lib.ue5m3_abi_version() != 2:
         raise NativeLibraryError("ABI version mismatch between the Python package and the library")
     _lib = lib
     return lib
@@ -102,12 +108,12 @@ def load() -> ctypes.CDLL:
 launch_count = 0  # successful kernel-launching library calls of this process
 
 
-def check(status: int, what: str) -> None:
-    """Raise on a non-zero status; every entry point checked here launches one kernel."""
+def check(status: int, what: str, launches: int = 1) -> None:
+    """Raise on a non-zero status; ``launches`` = kernels the successful call put on the stream."""
 
     global launch_count
     if status == UE5M3_OK:
-        launch_count += 1
+        launch_count += launches
         return
     lib = load()
     text = lib.ue5m3_status_string(status).decode()

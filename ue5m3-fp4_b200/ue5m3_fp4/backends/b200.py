@@ -292,22 +292,42 @@ def gemm_status(device: torch.device) -> Tensor:
     return words
 
 
-def check_gemm_status(device: torch.device) -> None:
-    """Synchronising check of the GEMM status words; raises if a wait expired."""
-
-    flag = _window_flags.get(device)
-    if flag is not None and int(flag.item()) != 0:
-        flag.zero_()
-        raise RuntimeError(
-            "a block scale fell outside the FP4 tensor core's scale window; the FP4 GEMM result is "
-            "invalid for that call - set UE5M3_GEMM_PATH=bf16 (issue-RZ kernel, no window)"
-        )
-    words = gemm_status(device).tolist()
+def _raise_on_status(words, device: torch.device) -> None:
     if words[0]:
         gemm_status(device).zero_()
         raise RuntimeError(
-            f"GEMM kernel gave up on a bounded wait (site {words[1]}, issue {words[2]}, tile {words[3]})"
+            f"GEMM kernel gave up on a bounded wait (site {words[1]}, issue {words[2]}, tile {words[3]}); "
+            "the outputs of that launch and of every GEMM launched after it are invalid"
         )
+
+
+def check_gemm_status(device: torch.device) -> None:
+    """Synchronising check of the GEMM status words; raises if a wait expired."""
+
+    _raise_on_status(gemm_status(device).tolist(), device)
+
+
+_status_polls: dict[torch.device, tuple[Tensor, torch.cuda.Event]] = {}
+
+
+def poll_gemm_status(device: torch.device) -> None:
+    """Check of the GEMM status words that never blocks the host: looks at the copy requested by
+    the previous call (if it has arrived) and requests the next one.  ``TrainingScaleState.begin_step``
+    and the inference controller call it once per step / phase change, so a kernel that gave up on
+    a bounded wait stops the run within two steps instead of feeding unwritten outputs onward."""
+
+    pending = _status_polls.get(device)
+    if pending is not None:
+        host, event = pending
+        if not event.query():
+            return
+        _raise_on_status(host.tolist(), device)
+    else:
+        host = torch.empty(4, dtype=torch.int32, pin_memory=True)
+        event = torch.cuda.Event()
+    host.copy_(gemm_status(device), non_blocking=True)
+    event.record(torch.cuda.current_stream(device))
+    _status_polls[device] = (host, event)
 
 
 def gemm_issue_rz(
@@ -352,18 +372,14 @@ def gemm_issue_rz(
     return out
 
 
-_window_flags: dict[torch.device, Tensor] = {}
+FALLBACK_MAX_ROWS = 1024  # UE5M3_FALLBACK_MAX_ROWS of the C ABI
 
 
-def window_flag(device: torch.device) -> Tensor:
-    """Device int32[1] raised by pack_scales when a block scale does not fit the tensor core's
-    UE4M3 range at the chosen shift (the FP4 result is then invalid; use the BF16-issue GEMM)."""
+def new_window_record(rows: int, device: torch.device) -> Tensor:
+    """Zeroed window record of an operand with ``rows`` rows (layout: include/ue5m3_fp4.h): the
+    quantizer lists here the rows that hold a block scale outside the tensor core's UE4M3 range."""
 
-    flag = _window_flags.get(device)
-    if flag is None:
-        flag = torch.zeros(1, dtype=torch.int32, device=device)
-        _window_flags[device] = flag
-    return flag
+    return torch.zeros(_native.load().ue5m3_window_record_ints(rows), dtype=torch.int32, device=device)
 
 
 def scale_shift_for_target(scale_target: float) -> int:
@@ -373,21 +389,27 @@ def scale_shift_for_target(scale_target: float) -> int:
     return max(0, math.ceil(math.log2(scale_target / 448.0)))
 
 
-def pack_scales(scales: Tensor, *, rows: int, k: int, block_size: int, two_dimensional: bool, shift: int) -> Tensor:
-    """UE5M3 scale bytes of a K-major operand -> UE4M3 bytes in the tensor core's scale layout."""
+def pack_scales(scales: Tensor, *, rows: int, k: int, block_size: int, two_dimensional: bool, shift: int,
+                record: Tensor | None = None, want_raw: bool = False):
+    """UE5M3 scale bytes of a K-major operand -> UE4M3 bytes in the tensor core's scale layout
+    (and, with ``want_raw``, the unmodified bytes in the same layout).  ``record``: the operand's
+    window record; a fresh one is made when it is not given."""
 
     _require_cuda(scales, "scales")
     size = _native.load().ue5m3_packed_scales_bytes(rows, k)
     if size == 0:
         raise ValueError("K must be divisible by 64")
     out = torch.empty(size, dtype=torch.uint8, device=scales.device)
+    raw = torch.empty(size, dtype=torch.uint8, device=scales.device) if want_raw else None
+    if record is None:
+        record = new_window_record(rows, scales.device)
     with torch.cuda.device(scales.device):
         status = _native.load().ue5m3_pack_scales_ue4m3(
             scales.data_ptr(), rows, k, block_size, int(two_dimensional), shift, out.data_ptr(),
-            window_flag(scales.device).data_ptr(), _native.stream_ptr(scales.device),
+            _native.ptr(raw), record.data_ptr(), _native.stream_ptr(scales.device),
         )
     _native.check(status, "ue5m3_pack_scales_ue4m3")
-    return out
+    return (out, raw, record) if want_raw else out
 
 
 def gemm_fp4(
@@ -428,13 +450,25 @@ def gemm_path() -> str:
 
 @dataclass(slots=True)
 class Fp4Operand:
-    """A K-major packed GEMM operand: codes [rows, K/2], scales in the tensor-core layout."""
+    """A K-major packed GEMM operand: codes [rows, K/2], block scales in the tensor-core layout
+    (UE4M3, re-biased by ``shift``), the same scales as unmodified UE5M3 bytes, and the window
+    record that lists the rows where the two differ (a scale outside the UE4M3 window)."""
 
     codes: Tensor
     scale_factors: Tensor
     shift: int
     rows: int
     k: int
+    raw_scale_factors: Tensor | None = None
+    record: Tensor | None = None
+
+    def window_counts(self) -> tuple[int, int]:
+        """(rows listed for recomputation, 16-element units outside the window); synchronises."""
+
+        if self.record is None:
+            return (0, 0)
+        listed, units = self.record[:2].tolist()
+        return int(listed), int(units)
 
 
 def quantize_fp4_operand(
@@ -475,8 +509,9 @@ def quantize_fp4_operand(
     rows, k = (x.shape[1], x.shape[0]) if transposed else (x.shape[0], x.shape[1])
     codes = packed.codes_t if transposed else packed.codes
     scales = packed.scales_t if transposed else packed.scales
-    sf = pack_scales(scales, rows=rows, k=k, block_size=block_size, two_dimensional=blocking == BLOCK_2D, shift=shift)
-    return Fp4Operand(codes, sf, shift, rows, k)
+    sf, raw, record = pack_scales(scales, rows=rows, k=k, block_size=block_size,
+                                  two_dimensional=blocking == BLOCK_2D, shift=shift, want_raw=True)
+    return Fp4Operand(codes, sf, shift, rows, k, raw, record)
 
 
 def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tensor_amax: Tensor,
@@ -504,6 +539,8 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
         k, rows = x.shape
         codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
         sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
+        raw = torch.empty_like(sf)
+        record = new_window_record(rows, dev)
         if hadamard:
             if not x.is_contiguous() or k % 64:
                 raise ValueError("the transformed operand needs a contiguous tensor whose first dimension is a multiple of 64")
@@ -512,23 +549,25 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
                     x.data_ptr(), _native.dtype_code(x.dtype), k, rows, tensor_amax.data_ptr(), float(scale_target),
                     _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
                     _native.ptr(random_bits), _bits_code(random_bits), shift,
-                    codes.data_ptr(), sf.data_ptr(), window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+                    codes.data_ptr(), sf.data_ptr(), raw.data_ptr(), record.data_ptr(), _native.stream_ptr(dev),
                 )
             _native.check(status, "ue5m3_quantize_fp4_operand_t_rht")
-            return Fp4Operand(codes, sf, shift, rows, k)
+            return Fp4Operand(codes, sf, shift, rows, k, raw, record)
         with torch.cuda.device(dev):
             status = lib.ue5m3_quantize_fp4_operand_t(
                 x.data_ptr(), _native.dtype_code(x.dtype), k, rows, block_size, blocking,
                 tensor_amax.data_ptr(), float(scale_target),
                 _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
                 _native.ptr(random_bits), _bits_code(random_bits), shift,
-                codes.data_ptr(), sf.data_ptr(), window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+                codes.data_ptr(), sf.data_ptr(), raw.data_ptr(), record.data_ptr(), _native.stream_ptr(dev),
             )
         _native.check(status, "ue5m3_quantize_fp4_operand_t")
-        return Fp4Operand(codes, sf, shift, rows, k)
+        return Fp4Operand(codes, sf, shift, rows, k, raw, record)
     rows, k = x.shape
     codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
     sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, k), dtype=torch.uint8, device=dev)
+    raw = torch.empty_like(sf)
+    record = new_window_record(rows, dev)
     scales = None
     if want_scales:
         scale_rows = rows if blocking == BLOCK_ROW else (rows + block_size - 1) // block_size
@@ -539,11 +578,11 @@ def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tenso
             tensor_amax.data_ptr(), float(scale_target),
             _native.ROUND_STOCHASTIC_FAST if stochastic else _native.ROUND_TIES_TO_EVEN,
             _native.ptr(random_bits), _bits_code(random_bits), shift,
-            codes.data_ptr(), sf.data_ptr(), _native.ptr(scales),
-            window_flag(dev).data_ptr(), _native.stream_ptr(dev),
+            codes.data_ptr(), sf.data_ptr(), raw.data_ptr(), _native.ptr(scales),
+            record.data_ptr(), _native.stream_ptr(dev),
         )
     _native.check(status, "ue5m3_quantize_fp4_operand")
-    operand = Fp4Operand(codes, sf, shift, rows, k)
+    operand = Fp4Operand(codes, sf, shift, rows, k, raw, record)
     return (operand, scales) if want_scales else operand
 
 
@@ -565,10 +604,33 @@ def hadamard_amax_transposed(x: Tensor) -> Tensor:
 
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor | None = None,
                       bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
+    """FP4 tensor-core product of two packed operands, followed (stream-ordered, no host
+    synchronisation) by the recomputation of whatever their window records list: output rows
+    for A, output columns for B, everything when a list overflowed.  The recomputation runs the
+    issue-RZ BF16 instruction sequence on the exact encoded operands, so the result is the
+    reference model's for every UE5M3 scale (the reference has no scale window,
+    formats.py:125-134)."""
+
     if a.k != b.k:
         raise ValueError("a and b have incompatible K dimensions")
-    return gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
-                    shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype)
+    out = gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
+                   shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype)
+    if a.record is None or b.record is None or a.raw_scale_factors is None or b.raw_scale_factors is None:
+        raise ValueError("packed operands must carry their raw scales and window records")
+    lib = _native.load()
+    workspace = torch.empty(lib.ue5m3_gemm_fp4_fallback_workspace_bytes(a.rows, b.rows, a.k),
+                            dtype=torch.uint8, device=out.device)
+    with torch.cuda.device(out.device):
+        status = lib.ue5m3_gemm_fp4_fallback(
+            a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(),
+            b.codes.data_ptr(), b.raw_scale_factors.data_ptr(), b.record.data_ptr(),
+            a.rows, b.rows, a.k, int(bool(snap)), _native.ptr(alpha), _native.ptr(bias),
+            _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
+            _native.dtype_code(out_dtype), b.rows, workspace.data_ptr(), workspace.numel(),
+            gemm_status(out.device).data_ptr(), _native.stream_ptr(out.device),
+        )
+    _native.check(status, "ue5m3_gemm_fp4_fallback", launches=2)
+    return out
 
 
 def encoded_global_alpha(amax_a: Tensor, amax_b: Tensor, target_a: float, target_b: float) -> Tensor:
@@ -792,17 +854,13 @@ def probe_matched_fp4_gemm(
     alpha = encoded_global_alpha(amax_a, amax_b, float(scale_target_a), float(scale_target_b))
     blocking_b = BLOCK_2D if two_dimensional_b else BLOCK_COL
     if gemm_path() == "fp4":
-        flag = window_flag(a.device)
-        flag.zero_()
         op_a = quantize_fp4_operand(a, block_size=block_size, blocking=BLOCK_ROW, transposed=False,
                                     tensor_amax=amax_a, scale_target=float(scale_target_a), rounding=mode_a,
                                     random_bits=bits_a)
         op_b = quantize_fp4_operand(b, block_size=block_size, blocking=blocking_b, transposed=True,
                                     tensor_amax=amax_b, scale_target=float(scale_target_b), rounding=mode_b,
                                     random_bits=bits_b)
-        if int(flag.item()) == 0:  # every block scale fits the tensor core's scale type
-            return gemm_fp4_operands(op_a, op_b, snap=snap_to_1_over_1024, alpha=alpha, out_dtype=torch.float32)
-        flag.zero_()
+        return gemm_fp4_operands(op_a, op_b, snap=snap_to_1_over_1024, alpha=alpha, out_dtype=torch.float32)
     enc_a = quantize_packed(
         a, block_size=block_size, blocking=BLOCK_ROW, tensor_amax=amax_a, scale_target=float(scale_target_a),
         rounding=mode_a, random_bits=bits_a, packed=False, fake_domain="encoded", fake_dtype=torch.bfloat16,
@@ -832,7 +890,8 @@ __all__ = [
     "gemm_path",
     "pack_scales",
     "quantize_fp4_operand",
-    "window_flag",
+    "new_window_record",
+    "poll_gemm_status",
     "gemm_status",
     "issue_rz_bf16_gemm",
     "probe_matched_fp4_gemm",

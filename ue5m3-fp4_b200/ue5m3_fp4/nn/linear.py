@@ -307,14 +307,15 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
                 and x.shape[0] % 64 == 0):  # the weight-gradient GEMM reduces over the tokens
             # The weight-gradient GEMM reads X^T blocked along the tokens with the SAME held
             # reference, so its packed operand (0.5625 byte per element) can be made now and
-            # saved instead of the bf16 activations (2 bytes per element); the result is the
+            # saved instead of the bf16 activations (2 bytes per element; the packed form also keeps
+            # the unmodified UE5M3 scale bytes, 0.625 byte per element in all); the result is the
             # operand the backward would have built (the reference re-quantizes a saved bf16
             # copy, linear.py:346,385-398).
             xt = _encode_k_major(x, plan=plan, role="activation",
                                  reference=activation_rht_reference if rht else activation_reference,
                                  reduce_over_rows=True, two_dimensional=False, hadamard=rht)
             ctx.packed_activation = (xt.shift, xt.rows, xt.k)
-            ctx.save_for_backward(weight, xt.codes, xt.scale_factors)
+            ctx.save_for_backward(weight, xt.codes, xt.scale_factors, xt.raw_scale_factors, xt.record)
         else:
             ctx.save_for_backward(weight, inputs)
         return output.reshape(*inputs.shape[:-1], weight.shape[0])
@@ -329,9 +330,9 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         plan = _OperandPlan(owner)
         two_d = owner.recipe.two_dimensional_weights
         if ctx.packed_activation is not None:
-            weight, xt_codes, xt_scales = ctx.saved_tensors
+            weight, xt_codes, xt_scales, xt_raw_scales, xt_record = ctx.saved_tensors
             shift, rows, k = ctx.packed_activation
-            xt_saved = b200.Fp4Operand(xt_codes, xt_scales, shift, rows, k)
+            xt_saved = b200.Fp4Operand(xt_codes, xt_scales, shift, rows, k, xt_raw_scales, xt_record)
             x = None
         else:
             weight, inputs = ctx.saved_tensors
