@@ -71,3 +71,25 @@ def ulp_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
         return np.where(i < 0, -(i & 0x7FFFFFFF), i)
 
     return np.abs(key(a) - key(b))
+
+
+def accumulation_unit(enc_a: np.ndarray, enc_bt: np.ndarray, group: int = 64) -> np.ndarray:
+    """Per output, one fp32 ulp of the largest magnitude its accumulation passes through: the
+    sums of each ``group`` of consecutive reduction elements (64 = one issue, 16 = one BF16
+    tensor-core instruction), the running sum inside an issue and the running sum across
+    issues (float64 estimates).  Deviations between accumulation rules are stated in this unit."""
+
+    a = np.asarray(enc_a, dtype=np.float64)
+    b = np.asarray(enc_bt, dtype=np.float64)
+    k = a.shape[1]
+    largest = np.zeros((a.shape[0], b.shape[0]))
+    total = np.zeros_like(largest)
+    for issue in range(0, k, 64):
+        inside = np.zeros_like(largest)
+        for g in range(issue, issue + 64, group):
+            part = a[:, g:g + group] @ b[:, g:g + group].T
+            inside += part
+            largest = np.maximum(largest, np.maximum(np.abs(part), np.abs(inside)))
+        total += inside
+        largest = np.maximum(largest, np.abs(total))
+    return np.spacing(largest.astype(np.float32)).astype(np.float64)

@@ -1,0 +1,173 @@
+"""What the FP4 block-scaled tensor-core instruction does with a K=64 issue, pinned on packed
+operands that are fed to ue5m3_gemm_fp4 directly (no quantizer in the way).
+
+Measured rule, and the one these tests hold the kernel to bit for bit:
+    c <- RTZ32(c + exact sum of the 64 scaled products of the issue)
+i.e. one round-toward-zero per issue.  The reference's model (backends/triton/gemm.py:14-23,
+62-80; docs/technical_report/main.tex:744-775) rounds the issue partial to nearest first and
+then adds with round-toward-zero; the two are the same function whenever the issue partial is
+representable in fp32, which the first family below makes true while the sums ACROSS issues
+are inexact - so that family decides the cross-issue rounding direction.  The other families
+make the partials themselves inexact (blocks of one issue 2^-15 .. 2^+15 apart), permute K64
+groups (reproduce/diagnostics/run_native_gemm_oracle.py:128-152) and build near-cancelling
+rows (reproduce/diagnostics/run_final_grid_sweep.py:40-61)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_helpers import accumulation_unit, to_np
+from oracle import ue5m3_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float64)
+
+
+@pytest.fixture(scope="module")
+def b200():
+    from ue5m3_fp4.backends import b200 as module
+
+    assert module.available()
+    return module
+
+
+def _encoded(nibbles: np.ndarray, scale_bytes: np.ndarray) -> np.ndarray:
+    values = np.where(nibbles & 8, -1.0, 1.0) * E2M1[nibbles & 7]
+    return (values * np.repeat(o.scale_values(scale_bytes.astype(np.uint8)).astype(np.float64), 16, axis=1)).astype(np.float32)
+
+
+def _run_fp4(b200, nib_a, sc_a, nib_b, sc_b) -> np.ndarray:
+    dev = torch.device("cuda", 0)
+    m, k = nib_a.shape
+    n = nib_b.shape[0]
+
+    def pack(nib):
+        return torch.from_numpy((nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)).to(dev)
+
+    def atoms(sc, rows):
+        return b200.pack_scales(torch.from_numpy(sc.astype(np.uint8)).to(dev), rows=rows, k=k, block_size=16,
+                                two_dimensional=False, shift=0)
+
+    out = b200.gemm_fp4(pack(nib_a), atoms(sc_a, m), pack(nib_b), atoms(sc_b, n), m=m, n=n, k=k, shift_sum=0,
+                        snap=False, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    return to_np(out)
+
+
+def _family(seed, m, n, issues, blocks_per_issue, dense, exp_lo, exp_hi):
+    """Random packed operands: in every issue ``blocks_per_issue`` of the four 16-blocks are
+    non-zero (one element each, or all sixteen when ``dense``) with UE5M3 scale bytes whose
+    exponent field is uniform in [exp_lo, exp_hi] (the window at shift 0 is 9..23)."""
+
+    rng = np.random.default_rng(seed)
+    k = issues * 64
+    nib_a, nib_b = np.zeros((m, k), np.int64), np.zeros((n, k), np.int64)
+    sc_a, sc_b = np.full((m, k // 16), 0x78, np.int64), np.full((n, k // 16), 0x78, np.int64)
+    for j in range(issues):
+        for blk in rng.choice(4, blocks_per_issue, replace=False):
+            kb = j * 4 + blk
+            if dense:
+                nib_a[:, kb * 16:(kb + 1) * 16] = rng.integers(0, 16, (m, 16))
+                nib_b[:, kb * 16:(kb + 1) * 16] = rng.integers(0, 16, (n, 16))
+            else:
+                pos = kb * 16 + rng.integers(0, 16)
+                nib_a[:, pos] = rng.integers(1, 8, m) | (rng.integers(0, 2, m) << 3)
+                nib_b[:, pos] = rng.integers(1, 8, n) | (rng.integers(0, 2, n) << 3)
+            sc_a[:, kb] = np.minimum((rng.integers(exp_lo, exp_hi + 1, m) << 3) | rng.integers(0, 8, m), 190)
+            sc_b[:, kb] = np.minimum((rng.integers(exp_lo, exp_hi + 1, n) << 3) | rng.integers(0, 8, n), 190)
+    return nib_a, sc_a, nib_b, sc_b
+
+
+def test_round_toward_zero_between_issues(b200):
+    """One product per issue: every issue partial is exact (12 significant bits), the sums across
+    the 24 issues are not (37 binades of range), so only the cross-issue rule decides - and the
+    model and the measured rule coincide."""
+
+    nib_a, sc_a, nib_b, sc_b = _family(0, 256, 384, 24, 1, False, 9, 23)
+    got = _run_fp4(b200, nib_a, sc_a, nib_b, sc_b)
+    ea, eb = _encoded(nib_a, sc_a), _encoded(nib_b, sc_b)
+    model = o.gemm_issue_rz(ea, eb, snap=False)
+    assert np.array_equal(got, model)
+    assert np.array_equal(model, o.gemm_issue_rz(ea, eb, snap=False, native_rule=True))
+    nearest = np.zeros_like(model)
+    for j in range(24):  # the same chain with round-to-nearest adds
+        nearest = nearest + (ea[:, j * 64:(j + 1) * 64].astype(np.float64) @ eb[:, j * 64:(j + 1) * 64].astype(np.float64).T).astype(np.float32)
+    assert (model != nearest).mean() > 0.05  # the family does tell RTZ from RN
+
+
+@pytest.mark.parametrize("name,issues,blocks,dense,lo,hi", [
+    ("two blocks, one product each", 1, 2, False, 9, 23),
+    ("four blocks, one product each", 1, 4, False, 9, 23),
+    ("four dense blocks", 1, 4, True, 9, 23),
+    ("four dense blocks, four issues", 4, 4, True, 9, 23),
+    ("dense, sixteen issues, seven binades", 16, 4, True, 12, 18),
+    ("dense, narrow scales", 8, 4, True, 14, 16),
+])
+def test_one_rounding_toward_zero_per_issue(b200, name, issues, blocks, dense, lo, hi):
+    nib_a, sc_a, nib_b, sc_b = _family(len(name), 128, 256, issues, blocks, dense, lo, hi)
+    got = _run_fp4(b200, nib_a, sc_a, nib_b, sc_b)
+    ea, eb = _encoded(nib_a, sc_a), _encoded(nib_b, sc_b)
+    assert np.array_equal(got, o.gemm_issue_rz(ea, eb, snap=False, native_rule=True)), name
+    # distance to the reference's two-rounding model, per output, in ulps of the largest
+    # magnitude that output's accumulation passes through: at most one per issue
+    model = o.gemm_issue_rz(ea, eb, snap=False)
+    ratio = np.abs(got.astype(np.float64) - model.astype(np.float64)) / accumulation_unit(ea, eb)
+    print(f"{name}: differing from the two-rounding model {float((got != model).mean()):.4f}, max {ratio.max():.1f} units")
+    assert ratio.max() <= issues
+    if hi - lo <= 2:
+        assert np.array_equal(got, model)  # partials exact: the rules coincide
+
+
+def test_issue_group_permutations_change_the_result_as_the_rule_says(b200):
+    """The same K64 groups in three orders: the accumulation is order-dependent, and each
+    order equals the rule evaluated in that order."""
+
+    nib_a, sc_a, nib_b, sc_b = _family(7, 128, 128, 12, 2, True, 9, 23)
+    rng = np.random.default_rng(3)
+    results = []
+    for order in (np.arange(12), np.arange(12)[::-1].copy(), rng.permutation(12)):
+        def reorder(x, width):
+            return x.reshape(x.shape[0], 12, width)[:, order, :].reshape(x.shape[0], -1)
+        pa, pb = reorder(nib_a, 64), reorder(nib_b, 64)
+        qa, qb = reorder(sc_a, 4), reorder(sc_b, 4)
+        got = _run_fp4(b200, pa, qa, pb, qb)
+        assert np.array_equal(got, o.gemm_issue_rz(_encoded(pa, qa), _encoded(pb, qb), snap=False, native_rule=True))
+        results.append(got)
+    assert (results[0] != results[1]).any() and (results[0] != results[2]).any()
+
+
+def test_near_cancelling_rows(b200):
+    """Issue partials come in +v / -v pairs in shuffled order plus one small residual, so the
+    exact row sum is tiny while the accumulator passes through large values."""
+
+    rng = np.random.default_rng(11)
+    m, n, pairs = 128, 128, 8
+    issues = 2 * pairs + 1
+    k = issues * 64
+    nib_a, nib_b = np.zeros((m, k), np.int64), np.zeros((n, k), np.int64)
+    sc_a, sc_b = np.full((m, k // 16), 0x78, np.int64), np.full((n, k // 16), 0x78, np.int64)
+    slots = rng.permutation(2 * pairs)
+    for pair in range(pairs):
+        mag_a = rng.integers(1, 8, m)
+        mag_b = rng.integers(1, 8, n)
+        sa = (rng.integers(9, 24, m) << 3) | rng.integers(0, 8, m)
+        sb = (rng.integers(12, 19, n) << 3) | rng.integers(0, 8, n)
+        for sign, slot in ((0, slots[2 * pair]), (8, slots[2 * pair + 1])):
+            nib_a[:, slot * 64] = mag_a | sign      # the sign flips on A only: partials +v and -v
+            nib_b[:, slot * 64] = mag_b
+            sc_a[:, slot * 4] = np.minimum(sa, 190)
+            sc_b[:, slot * 4] = np.minimum(sb, 190)
+    nib_a[:, (issues - 1) * 64] = rng.integers(1, 8, m) | (rng.integers(0, 2, m) << 3)   # the residual
+    nib_b[:, (issues - 1) * 64] = rng.integers(1, 8, n)
+    sc_a[:, (issues - 1) * 4] = 9 << 3
+    sc_b[:, (issues - 1) * 4] = 12 << 3
+    got = _run_fp4(b200, nib_a, sc_a, nib_b, sc_b)
+    ea, eb = _encoded(nib_a, sc_a), _encoded(nib_b, sc_b)
+    expect = o.gemm_issue_rz(ea, eb, snap=False)
+    assert np.array_equal(got, expect)  # single products: partials exact, model = measured rule
+    exact = ea.astype(np.float64) @ eb.astype(np.float64).T
+    assert (np.abs(got - exact) > 0).mean() > 0.2  # the rounding of the large intermediates does show

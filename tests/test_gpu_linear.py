@@ -156,6 +156,54 @@ def test_inference_lifecycle_current_tensor_and_frozen():
     assert controller.counters()["proj"]["activation_frozen_resolutions"] == 1
 
 
+def test_inference_lifecycle_training_replay():
+    """Post-load inference that replays the D = 50 training cadence: the activation amax is
+    sampled at work units 1 and 51 and held in between (nn/linear.py:575-598 of the reference),
+    every forward is preceded by one work-unit advancement, and a second forward inside one
+    work unit is refused."""
+
+    from ue5m3_fp4.scaling import FP4InferenceScalingController
+
+    model = torch.nn.Sequential()
+    model.add_module("proj", _layer(128, 64, bias=False, name="proj"))
+    model.eval()
+    with pytest.raises(ValueError, match="replay_work_unit"):
+        FP4InferenceScalingController(model, activation_mode="training_replay", checkpoint_identity={"name": "synthetic"})
+    controller = FP4InferenceScalingController(
+        model, activation_mode="training_replay", checkpoint_identity={"name": "synthetic"},
+        replay_work_unit={"kind": "fixed_forward_batch", "size": 32})
+    controller.reset_after_checkpoint_load()
+    controller.calibrate_and_freeze_weights()
+    with pytest.raises(ValueError, match="evaluation_order"):
+        controller.begin_measurement()
+    controller.begin_measurement(evaluation_order={"order": "sequential", "seed": 0})
+    g = torch.Generator(device="cuda").manual_seed(3)
+    ids = torch.zeros(32, 8, dtype=torch.int64, device="cuda")
+    with torch.no_grad():
+        with pytest.raises(RuntimeError, match="Advance the replay work unit"):
+            model(torch.randn(32, 128, device="cuda", generator=g).to(torch.bfloat16))
+        amaxes, outputs = {}, {}
+        for unit in range(1, 53):
+            x = (torch.randn(32, 128, device="cuda", generator=g) * (1 + unit % 5)).to(torch.bfloat16)
+            controller.advance_training_replay_work_unit(ids + unit, effective_token_count=256)
+            outputs[unit] = model(x)
+            amaxes[unit] = x.float().abs().max().item()
+            if unit == 7:
+                with pytest.raises(RuntimeError, match="consumed twice"):
+                    model(x)
+        with pytest.raises(ValueError, match="fixed forward batch"):
+            controller.advance_training_replay_work_unit(ids[:5], effective_token_count=40)
+    report = model.proj.fp4_inference_scaling_report()["training_replay"]
+    assert [entry["logical_step"] for entry in report["refresh_trace"]["forward.x"]] == [1, 51]
+    assert [entry["amax"] for entry in report["refresh_trace"]["forward.x"]] == [amaxes[1], amaxes[51]]
+    assert report["last_consumed_step"] == 52 and report["cache"]["forward.x"] == amaxes[51]
+    counters = controller.counters()["proj"]
+    assert counters["activation_replay_refreshes"] == 2 and counters["activation_replay_reuses"] == 50
+    assert len(controller.training_replay_work_units) == 52
+    # a held step really quantizes with the amax of work unit 1: same input, other reference -> other output
+    assert outputs[2].shape == (32, 64) and torch.isfinite(outputs[2].float()).all()
+
+
 def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monkeypatch):
     """On the FP4 path the forward saves the packed weight-gradient operand of X (codes +
     scale atoms, the raw scale bytes and the small window record) instead of the bf16

@@ -197,6 +197,30 @@ def test_headline_shape_stochastic_quantize_full_size(b200):
     assert torch.equal(back, got.fake)
 
 
+def test_round_trip_configuration_full_size(b200):
+    """fp32 4096 x 4096, N(0,1) with a seeded 1 % of the entries multiplied by 100, B=16 along
+    the last axis, target 448 from the CURRENT tensor's amax (D=1, taken by ue5m3_amax), ties to
+    even: packed nibble codes, UE5M3 scale bytes and the dequantized fp32 tensor, every element
+    against the oracle; the packed form alone dequantizes to the same tensor."""
+
+    x = outlier_normal(4096, 4096, seed=0)
+    xd = x.cuda()
+    amax = b200.tensor_amax(xd).reshape(1)
+    assert amax.item() == x.abs().max().item()
+    got = b200.quantize_packed(xd, block_size=16, tensor_amax=amax, scale_target=448.0, rounding="TTE",
+                               fake_domain="dequant", fake_dtype=torch.float32)
+    q = oracle_quantize(x, block=16, blocking=o.BLOCK_ROW, amax=float(amax.item()))
+    assert got.codes.shape == (4096, 2048) and got.scales.shape == (4096, 256)
+    assert np.array_equal(to_np(got.codes), o.pack_nibbles(q["nibbles"]))
+    assert np.array_equal(to_np(got.scales), q["scale_codes"])
+    assert np.array_equal(to_np(got.fake), q["dequant"])
+    back = b200.dequantize_packed(got.codes, got.scales, rows=4096, cols=4096, block_size=16,
+                                  two_dimensional=False, tensor_amax=amax)
+    assert torch.equal(back, got.fake)
+    # the outliers do stretch the block scales over many binades (UE5M3's reason for being)
+    assert int(q["scale_codes"].max()) - int(q["scale_codes"].min()) >= 6 * 8
+
+
 def test_entry_point_contract_of_the_reference(b200):
     from ue5m3_fp4.backends.triton import fake_quantize_gemm_operands
 
