@@ -155,8 +155,12 @@ int ue5m3_alpha(const float *amax_a, const float *amax_b, float inv_denominator,
  *   out[M,N] = epilogue( A[M,K] * Bt[N,K]^T )
  * One tcgen05 issue per 64 reduction elements into a fresh TMEM accumulator;
  * issue partials are combined in ascending k with fp32 round-toward-zero adds;
- * then, fused: optional RNE snap to the 1/1024 grid, * alpha[0] (device scalar,
- * NULL = 1), + bias[n] (fp32 or bf16, NULL = none), cast to out_dtype.
+ * then, fused: optional RNE snap to the 1/1024 grid, * alpha, + bias[n] (fp32 or bf16,
+ * NULL = none), cast to out_dtype.  alpha is either alpha_dev[0] (device scalar), or, when
+ * alpha_dev is NULL and amax_a_dev / amax_b_dev are given, fl(fl(amax_a[0] * amax_b[0]) *
+ * inv_denominator) formed in the epilogue from the two held tensor amaxes (device scalars) and
+ * the host-computed fp32 reciprocal of (Ta*6)*(Tb*6) - the expression of
+ * backends/triton/quantization.py:412-420 as ATen evaluates it - or 1 when all three are NULL.
  * Replaces: backends/triton/gemm.py:26-88,110-160 (_issue_rz_kernel,
  * issue_rz_bf16_gemm), api.py:72-83 and nn/linear.py:334-336.
  * K % 64 == 0; a, bt 16-byte aligned; ldo = row stride of out in elements.
@@ -164,7 +168,8 @@ int ue5m3_alpha(const float *amax_a, const float *amax_b, float inv_denominator,
  * kernel expired; the kernel then returns without writing the affected tile.
  */
 int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N, int64_t K,
-                             int snap, const float *alpha_dev, const void *bias,
+                             int snap, const float *alpha_dev, const float *amax_a_dev,
+                             const float *amax_b_dev, float inv_denominator, const void *bias,
                              int bias_dtype, void *out, int out_dtype, int64_t ldo,
                              int *status_dev, void *stream);
 
@@ -261,7 +266,8 @@ int ue5m3_quantize_fp4_operand_t_rht(const void *x, int dtype, int64_t rows, int
  */
 int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                    const uint8_t *b_sf, int64_t M, int64_t N, int64_t K, int shift_sum, int snap,
-                   const float *alpha_dev, const void *bias, int bias_dtype, void *out,
+                   const float *alpha_dev, const float *amax_a_dev, const float *amax_b_dev,
+                   float inv_denominator, const void *bias, int bias_dtype, void *out,
                    int out_dtype, int64_t ldo, int *status_dev, void *stream);
 
 /*
@@ -269,22 +275,19 @@ int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
  * after ue5m3_gemm_fp4 on the same stream with the same epilogue arguments, it overwrites
  * the output rows listed in a_record and the output columns listed in b_record (everything,
  * when a list overflowed) with the result of the issue-RZ kernel of ue5m3_gemm_issue_rz_bf16
- * on the exact encoded operands, which it decodes from the codes and the raw UE5M3 scale
- * atoms (sf_raw of the quantizers).  The records are read on the device: no host
- * synchronisation, and with empty records the two launches return at once.  This is what
- * makes the FP4 path produce the reference model's result for every tensor the reference
- * accepts (its UE5M3 scales have no window, formats.py:125-134,
- * backends/triton/quantization.py:116-127).
- * workspace: ue5m3_gemm_fp4_fallback_workspace_bytes(M, N, K) bytes, 16-byte aligned,
- * contents undefined before and after.
+ * on the exact encoded operands, which its producer warps decode from the codes and the raw
+ * UE5M3 scale atoms (sf_raw of the quantizers) straight into shared memory.  The records are
+ * read on the device: no host synchronisation, no workspace, and with empty records the one
+ * launch returns at once.  This is what makes the FP4 path produce the reference model's
+ * result for every tensor the reference accepts (its UE5M3 scales have no window,
+ * formats.py:125-134, backends/triton/quantization.py:116-127).
  */
-size_t ue5m3_gemm_fp4_fallback_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int ue5m3_gemm_fp4_fallback(const uint8_t *a_codes, const uint8_t *a_sf_raw, const int *a_record,
                             const uint8_t *b_codes, const uint8_t *b_sf_raw, const int *b_record,
                             int64_t M, int64_t N, int64_t K, int snap, const float *alpha_dev,
-                            const void *bias, int bias_dtype, void *out, int out_dtype,
-                            int64_t ldo, void *workspace, size_t workspace_bytes,
-                            int *status_dev, void *stream);
+                            const float *amax_a_dev, const float *amax_b_dev,
+                            float inv_denominator, const void *bias, int bias_dtype, void *out,
+                            int out_dtype, int64_t ldo, int *status_dev, void *stream);
 
 /*
  * Test hook: compares the software E2M1 ties-to-even rounding with the sm_100a

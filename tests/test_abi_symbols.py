@@ -43,9 +43,6 @@ def test_version_and_status_strings():
     lib.ue5m3_window_record_ints.restype = ctypes.c_size_t
     lib.ue5m3_window_record_ints.argtypes = [ctypes.c_int64]
     assert lib.ue5m3_window_record_ints(300) == 4 + 1024 + 300
-    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.restype = ctypes.c_size_t
-    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.argtypes = [ctypes.c_int64] * 3
-    assert lib.ue5m3_gemm_fp4_fallback_workspace_bytes(128, 256, 64) == (128 + 256 + 2048) * 64 * 2
 
 
 def test_argument_validation_needs_no_device():
@@ -66,6 +63,9 @@ def test_argument_validation_needs_no_device():
     assert call(rounding=7) == 1  # stochastic without bits
     assert call(bits=fake) == 1  # bits with ties-to-even
     assert call(target=0.0) == 1
-    lib.ue5m3_gemm_issue_rz_bf16.argtypes = [p, p, i64, i64, i64, i32, p, p, i32, p, i32, i64, p, p]
-    assert lib.ue5m3_gemm_issue_rz_bf16(fake, fake, 8, 8, 65, 0, None, None, 0, fake, 1, 8, None, None) == 3
-    assert lib.ue5m3_gemm_issue_rz_bf16(fake + 2, fake, 8, 8, 64, 0, None, None, 0, fake, 1, 8, None, None) == 4
+    lib.ue5m3_gemm_issue_rz_bf16.argtypes = [p, p, i64, i64, i64, i32, p, p, p, f32, p, i32, p, i32, i64, p, p]
+    assert lib.ue5m3_gemm_issue_rz_bf16(fake, fake, 8, 8, 65, 0, None, None, None, 0.0, None, 0, fake, 1, 8, None, None) == 3
+    assert lib.ue5m3_gemm_issue_rz_bf16(fake + 2, fake, 8, 8, 64, 0, None, None, None, 0.0, None, 0, fake, 1, 8, None, None) == 4
+    # alpha comes either as a ready scalar or as two amax scalars, never both, never one amax alone
+    assert lib.ue5m3_gemm_issue_rz_bf16(fake, fake, 8, 8, 64, 0, fake, fake, fake, 1.0, None, 0, fake, 1, 8, None, None) == 1
+    assert lib.ue5m3_gemm_issue_rz_bf16(fake, fake, 8, 8, 64, 0, None, fake, None, 1.0, None, 0, fake, 1, 8, None, None) == 1

@@ -47,7 +47,12 @@ def _worker(rank: int, world: int, port: int, results) -> None:
             state.begin_step(step)
             local = torch.tensor([10.0 * step + rank])
             seen.append(state.reference("activation", "layers.0.mixer.up_proj", local).item())
-        results[rank] = (value.item(), seen, calls["n"])
+        # all weights due at a step: one collective for the whole vector
+        before = calls["n"]
+        state.begin_step(60)
+        sampled = state.sample_weights([(f"w{i}", torch.full((2, 2), float(10 * i + rank))) for i in range(4)])
+        held = [state.reference("weight", f"w{i}", torch.zeros(2, 2)).item() for i in range(4)]
+        results[rank] = (value.item(), seen, before, sampled, held, calls["n"] - before)
     finally:
         dist.destroy_process_group()
 
@@ -58,8 +63,9 @@ def test_two_gloo_ranks_share_the_global_amax_and_the_refresh_cadence():
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     for rank in range(world):
-        value, seen, collectives = results[rank]
+        value, seen, collectives, sampled, held, weight_collectives = results[rank]
         assert value == 2.0  # max over ranks of (rank + 1)
         # refresh at steps 1 and 51 takes the max over ranks; steps 2 and 50 hold step 1's value
         assert seen == [11.0, 11.0, 11.0, 511.0]
         assert collectives == 3  # one direct sample + two refreshes; hold steps use no collective
+        assert sampled == 4 and held == [1.0, 11.0, 21.0, 31.0] and weight_collectives == 1

@@ -344,6 +344,40 @@ def test_an_overflowing_window_record_recomputes_the_whole_product(b200, monkeyp
     assert torch.equal(got, expect)
 
 
+def test_alpha_formed_in_the_epilogue_equals_the_aten_expression(b200):
+    """EpilogueAlpha (two amax scalars + the fp32 reciprocal, combined inside the kernels)
+    against the explicit alpha tensor of backends/triton/quantization.py:412-420, on both GEMM
+    kernels and through the recomputation pass."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(77)
+    a = torch.randn(160, 256, generator=g)
+    a[3, 32:48] *= 2.0 ** -21      # one listed row, so that the recomputation pass writes too
+    a = a.to(torch.bfloat16).cuda()
+    bt = (0.02 * torch.randn(300, 256, generator=g)).to(torch.bfloat16).cuda()
+    for ta, tb in ((448.0, 448.0), (2048.0, 448.0)):
+        amax_a, amax_b = b200.tensor_amax(a).reshape(1) * 1.37, b200.tensor_amax(bt).reshape(1)
+        explicit = b200.encoded_global_alpha(amax_a, amax_b, ta, tb)
+        fused = b200.EpilogueAlpha.of(amax_a, amax_b, ta, tb)
+        op_a = b200.quantize_fp4_operand(a, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax_a,
+                                         scale_target=ta, shift_headroom=1)
+        op_b = b200.quantize_fp4_operand(bt, block_size=16, blocking=b200.BLOCK_2D, transposed=False, tensor_amax=amax_b,
+                                         scale_target=tb)
+        assert op_a.window_counts()[0] == 1
+        one = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=explicit, out_dtype=torch.bfloat16)
+        two = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=fused, out_dtype=torch.bfloat16)
+        assert torch.equal(one, two)
+        enc_a = b200.quantize_packed(a, block_size=16, tensor_amax=amax_a, scale_target=ta, packed=False,
+                                     fake_domain="encoded", fake_dtype=torch.bfloat16).fake
+        enc_b = b200.quantize_packed(bt, block_size=16, blocking=b200.BLOCK_2D, tensor_amax=amax_b, scale_target=tb,
+                                     packed=False, packed_t=False, fake_domain="encoded", fake_dtype=torch.bfloat16).fake
+        one = b200.gemm_issue_rz(enc_a, enc_b, snap=True, alpha=explicit)
+        two = b200.gemm_issue_rz(enc_a, enc_b, snap=True, alpha=fused)
+        assert torch.equal(one, two)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+
+
 def _listed(op) -> list[int]:
     count = min(op.window_counts()[0], 1024)
     return sorted(op.record[4:4 + count].tolist())

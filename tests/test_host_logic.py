@@ -93,6 +93,51 @@ def test_d50_is_sample_and_hold_not_a_window_maximum(host_sampler):
     assert state.state_dict() == {}
 
 
+def test_non_finite_samples_stop_the_run_at_the_next_step(host_sampler):
+    """The finite check of a sampled amax is deferred: no host read at sampling time, one for
+    all samples of a step when the next step begins (or on verify_samples / report)."""
+
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    state.begin_step(1)
+    assert state.reference("activation", "a", torch.tensor([2.0])).item() == 2.0
+    bad = state.reference("upstream_gradient", "a", torch.tensor([1.0, float("nan")]))
+    assert torch.isnan(bad)  # handed out as sampled
+    with pytest.raises(ValueError, match=r"non-finite values \(upstream_gradient:a\)"):
+        state.begin_step(2)
+    state.begin_step(2)  # the offending samples were reported once
+    state.reference("weight", "b", torch.tensor([float("inf")]))
+    with pytest.raises(ValueError, match="weight:b"):
+        state.verify_samples()
+
+
+def test_weights_are_sampled_together_before_the_forward_pass(monkeypatch, host_sampler):
+    calls = []
+
+    def fake_all_reduce(tensor, op=None):
+        calls.append((tuple(tensor.shape), op))
+        tensor.mul_(2.0)  # stands for a larger value on another rank
+
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda: 4)
+    monkeypatch.setattr(dist, "get_backend", lambda: "gloo")
+    monkeypatch.setattr(dist, "all_reduce", fake_all_reduce)
+    state = TrainingScaleState(UE5M3Recipe.proposed())
+    with pytest.raises(RuntimeError, match="begin_step"):
+        state.sample_weights([("a", torch.ones(2))])
+    state.begin_step(1)
+    weights = [(f"layers.{i}.mixer.up_proj", torch.full((3, 3), float(i + 1))) for i in range(5)]
+    assert state.sample_weights(weights) == 5
+    assert calls == [((5,), dist.ReduceOp.MAX)]  # one collective for the five weights
+    calls.clear()
+    # the linears' own lookups now find the values held: no sampling, no collective
+    assert state.reference("weight", "layers.3.mixer.up_proj", torch.zeros(3, 3)).item() == 8.0
+    assert calls == [] and state.sample_weights(weights) == 0
+    state.begin_step(51)
+    assert state.sample_weights(weights[:2]) == 2 and calls == [((2,), dist.ReduceOp.MAX)]
+    entries = {e["module_name"]: e for e in state.report()["entries"]}
+    assert entries["layers.0.mixer.up_proj"]["refreshes"] == 2 and entries["layers.4.mixer.up_proj"]["refreshes"] == 1
+
+
 def test_keys_are_per_role_and_module_and_cadence_starts_at_first_use(host_sampler):
     state = TrainingScaleState(UE5M3Recipe.proposed())
     state.begin_step(7)

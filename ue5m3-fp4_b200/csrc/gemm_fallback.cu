@@ -2,28 +2,31 @@
 // sequence of gemm_sm100.cu, the part of the output that the FP4 kernel could not get right
 // because a UE5M3 block scale fell outside the tensor core's UE4M3 window.
 //
-// The quantizers list such operand rows in a window record (include/ue5m3_fp4.h).  Everything
-// here is driven by those records ON THE DEVICE, so the host launches the same two kernels
-// after every FP4 GEMM without looking at the data:
-//   1. decode_operands_kernel: E2M1 codes x raw UE5M3 scale atoms -> encoded bf16 values
-//      (p * s is exact in bf16).  Listed rows of A go to a compact [1024, K] buffer, and then B
-//      is decoded in full, because a listed output row needs every column; the same with the
-//      roles swapped for listed rows of B (= output columns).
-//   2. gemm_fallback_kernel: persistent CTAs walk the tiles of up to three products,
-//      (listed A rows) x B -> scattered to those output rows, A x (listed B rows) -> scattered
-//      to those output columns, or, when a list overflowed, A x B over the whole output.
-//      Per tile it is the kernel of gemm_sm100.cu: TMA -> 4-stage ring -> four K=16 BF16 MMAs
-//      into a fresh TMEM accumulator per K=64 issue -> round-toward-zero adds in registers ->
-//      snap, alpha, bias, cast.  The issue counter runs on across tiles, so the mbarrier
-//      phases never need re-initialising.
-// With empty records both kernels return after reading two integers.
+// The quantizers list such operand rows in a window record (include/ue5m3_fp4.h).  The kernel
+// is driven by those records ON THE DEVICE, so the host launches it after every FP4 GEMM
+// without looking at the data; with empty records every CTA returns after reading two integers.
+//
+// Persistent CTAs walk the tiles of up to three products,
+//   (listed A rows) x B            -> scattered to those output rows,
+//   A x (listed B rows)            -> scattered to those output columns,
+//   A x B over the whole output    -> when a list overflowed its capacity,
+// and per tile do what gemm_sm100.cu does: four K=16 BF16 MMAs into a fresh TMEM accumulator
+// per K=64 issue, round-toward-zero adds across issues in registers, then snap, alpha, bias,
+// cast.  The operands are not read as bf16 from memory: three producer warps decode the packed
+// E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
+// 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
+// the record.  No workspace, no separate decode pass.  The issue counter runs on across tiles,
+// so the mbarrier phases never need re-initialising.
+//
+// Warps: 0..2 producers, 3 MMA issuer and TMEM owner, 4..11 epilogue (TMEM lane quadrant =
+// warp % 4, column half = (warp - 4) / 4).  Every wait is clock-bounded.
 #include <cuda.h>
-#include <cudaTypedefs.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "abi_common.cuh"
+#include "alpha_spec.cuh"
 #include "tcgen05_ptx.cuh"
 #include "ue5m3_device.cuh"
 #include "window_record.cuh"
@@ -38,22 +41,25 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 320;
+constexpr int kProducerWarps = 3;
+constexpr int kMmaWarp = kProducerWarps;
+constexpr int kEpilogueWarp0 = kMmaWarp + 1;
 constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 32 * (kEpilogueWarp0 + kEpilogueWarps);
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kStageBytesA = kBM * kBK * 2;
 constexpr uint32_t kStageBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
 
 struct Plan {
-    int na, nb;        // listed rows of A / of B, clamped to the capacity
+    int na, nb;        // listed rows of A / of B (0 when a list overflowed)
     bool full;         // a list overflowed: recompute everything
     int tiles[3];      // tiles of the row pass, the column pass, the full pass
 };
 
 __device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, int M, int N) {
     Plan plan;
-    const int na = rec_a ? __ldg(rec_a) : 0, nb = rec_b ? __ldg(rec_b) : 0;
+    const int na = __ldg(rec_a), nb = __ldg(rec_b);
     plan.full = na > kRecMaxRows || nb > kRecMaxRows;
     plan.na = plan.full ? 0 : na;
     plan.nb = plan.full ? 0 : nb;
@@ -64,66 +70,20 @@ __device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, in
     return plan;
 }
 
-struct DecodeArgs {
-    const uint8_t* codes[2];   // A, B: [rows, K / 2]
-    const uint8_t* raw[2];     // raw UE5M3 scale atoms
-    const int* rec[2];
-    int rows[2];               // M, N
-    int K;
-    __nv_bfloat16* compact[2]; // [kRecMaxRows, K]
-    __nv_bfloat16* full[2];    // [rows, K]
-};
-
-// eight codes (one 32-bit word) x one scale -> eight bf16 values
-__device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
-    uint32_t out[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float lo = __fmul_rn(e2m1_value((word >> (8 * i)) & 0xFu), scale);
-        const float hi = __fmul_rn(e2m1_value((word >> (8 * i + 4)) & 0xFu), scale);
-        out[i] = float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
-    }
-    return make_uint4(out[0], out[1], out[2], out[3]);
-}
-
-__device__ __forceinline__ void decode_rows(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ raw,
-                                            const int* __restrict__ list, int64_t nrows, int K,
-                                            __nv_bfloat16* __restrict__ out) {
-    const int64_t words_per_row = K / 8;
-    const int64_t k_atoms = K / 64;
-    const int64_t total = nrows * words_per_row;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t slot = idx / words_per_row, w = idx % words_per_row;
-        const int64_t row = list ? (int64_t)__ldg(list + slot) : slot;
-        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (K / 2)) + w);
-        const int64_t k = w * 8;
-        const uint8_t byte = __ldg(raw + ((row >> 7) * k_atoms + (k >> 6)) * 512 + (row & 31) * 16 +
-                                   ((row >> 5) & 3) * 4 + ((k >> 4) & 3));
-        *reinterpret_cast<uint4*>(out + slot * K + k) = decode_word(word, ue5m3_decode(byte));
-    }
-}
-
-__global__ void __launch_bounds__(256) decode_operands_kernel(const DecodeArgs a) {
-    const Plan plan = make_plan(a.rec[0], a.rec[1], a.rows[0], a.rows[1]);
-    if (plan.na > 0)
-        decode_rows(a.codes[0], a.raw[0], a.rec[0] + kRecHeader, plan.na, a.K, a.compact[0]);
-    if (plan.nb > 0)
-        decode_rows(a.codes[1], a.raw[1], a.rec[1] + kRecHeader, plan.nb, a.K, a.compact[1]);
-    if (plan.full || plan.nb > 0) decode_rows(a.codes[0], a.raw[0], nullptr, a.rows[0], a.K, a.full[0]);
-    if (plan.full || plan.na > 0) decode_rows(a.codes[1], a.raw[1], nullptr, a.rows[1], a.K, a.full[1]);
-}
-
 struct Params {
     int M, N, K;
     int snap;
-    const float* alpha;
+    AlphaSpec alpha;
     const void* bias;
     int bias_dtype;
     void* out;
     int out_dtype;
     long long ldo;
     int* status;
+    const uint8_t* codes_a;   // [M, K / 2]
+    const uint8_t* codes_b;   // [N, K / 2]
+    const uint8_t* raw_a;     // raw UE5M3 scale atoms
+    const uint8_t* raw_b;
     const int* rec_a;
     const int* rec_b;
 };
@@ -161,6 +121,11 @@ __device__ __forceinline__ void fadd2_rz(float& c0, float& c1, uint32_t v0, uint
         : "r"(v0), "r"(v1));
 }
 
+// writes made with ordinary shared-memory stores become visible to the tensor core's reads
+__device__ __forceinline__ void fence_generic_to_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
@@ -191,6 +156,41 @@ __device__ __forceinline__ Tile locate_tile(const Plan& plan, int t, int M, int 
     tile.job = 2; tile.m0 = (t / tiles_n) * kBM; tile.n0 = (t % tiles_n) * kBN;
     tile.rows = M; tile.cols = N;
     return tile;
+}
+
+// eight codes (one 32-bit word) x one scale -> eight bf16 values
+__device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
+    uint32_t out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = __fmul_rn(e2m1_value((word >> (8 * i)) & 0xFu), scale);
+        const float hi = __fmul_rn(e2m1_value((word >> (8 * i + 4)) & 0xFu), scale);
+        out[i] = float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// One K=64 slab of `tile_rows` operand rows -> bf16 in the 128-byte-swizzled K-major layout:
+// row r occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk position c ^ (r & 7).
+// `first` = first local row, `count` = rows that exist (others become zero), `list` maps local
+// rows to operand rows (null: identity).
+__device__ __forceinline__ void produce_slab(unsigned char* smem_tile, int tile_rows, const uint8_t* __restrict__ codes,
+                                             const uint8_t* __restrict__ raw, const int* __restrict__ list, int first,
+                                             int count, int K, int issue, int producer_thread) {
+    const int64_t k_atoms = K / 64;
+    for (int item = producer_thread; item < tile_rows * 8; item += kProducerWarps * 32) {
+        const int r = item >> 3, c = item & 7;   // row of the tile, 8-element chunk of the issue
+        const int local = first + r;
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (local < count) {
+            const int64_t row = list ? (int64_t)__ldg(list + local) : local;
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (K / 2) + issue * 32) + c);
+            const uint8_t byte = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 +
+                                       ((row >> 5) & 3) * 4 + (c >> 1));
+            value = decode_word(word, ue5m3_decode(byte));
+        }
+        *reinterpret_cast<uint4*>(smem_tile + r * 128 + ((c ^ (r & 7)) << 4)) = value;
+    }
 }
 
 template <typename OutT>
@@ -225,11 +225,7 @@ __device__ __forceinline__ void store_row(const Params& p, const Tile& tile, con
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
-                     const __grid_constant__ CUtensorMap map_b_full,
-                     const __grid_constant__ CUtensorMap map_a_full,
-                     const __grid_constant__ CUtensorMap map_b_compact, const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params p) {
     const Plan plan = make_plan(p.rec_a, p.rec_b, p.M, p.N);
     const int total_tiles = plan.tiles[0] + plan.tiles[1] + plan.tiles[2];
     if ((int)blockIdx.x >= total_tiles) return;  // the whole CTA, before anything is set up
@@ -245,7 +241,7 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->full[s], kProducerWarps);
             mbar_init(&bars->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -256,7 +252,7 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
         bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(&bars->tmem_base, kTmemCols);
+    if (warp == kMmaWarp) tmem_alloc(&bars->tmem_base, kTmemCols);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -265,31 +261,31 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
 
     if (dead) {
         // fall through to the common exit
-    } else if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            int g = 0;  // issues since the kernel started, over all tiles of this CTA
-            bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const Tile tile = locate_tile(plan, t, p.M, p.N);
-                const CUtensorMap* ma = tile.job == 0 ? &map_a_compact : &map_a_full;
-                const CUtensorMap* mb = tile.job == 1 ? &map_b_compact : &map_b_full;
-                for (int j = 0; j < num_issues; ++j, ++g) {
-                    const int s = g % kStages;
-                    const uint32_t use = g / kStages;
-                    if (use > 0 && !mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g)) {
-                        ok = false;
-                        break;
-                    }
-                    unsigned char* sa = smem + s * kStageBytes;
-                    unsigned char* sb = sa + kStageBytesA;
-                    mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
-                    tma_load_2d(sa, ma, &bars->full[s], j * kBK, tile.m0);
-                    tma_load_2d(sb, mb, &bars->full[s], j * kBK, tile.n0);
+    } else if (warp < kProducerWarps) {
+        // ---------------- producers: decode packed operands into the stage ----------------
+        int g = 0;  // issues since the kernel started, over all tiles of this CTA
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const Tile tile = locate_tile(plan, t, p.M, p.N);
+            const int* list_a = tile.job == 0 ? p.rec_a + kRecHeader : nullptr;
+            const int* list_b = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
+            for (int j = 0; j < num_issues; ++j, ++g) {
+                const int s = g % kStages;
+                const uint32_t use = g / kStages;
+                if (use > 0) {
+                    ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
+                    if (!ok) break;
                 }
+                unsigned char* sa = smem + s * kStageBytes;
+                produce_slab(sa, kBM, p.codes_a, p.raw_a, list_a, tile.m0, tile.rows, p.K, j, threadIdx.x);
+                produce_slab(sa + kStageBytesA, kBN, p.codes_b, p.raw_b, list_b, tile.n0, tile.cols, p.K, j, threadIdx.x);
+                fence_generic_to_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full[s]);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(kBM, kBN);
@@ -324,8 +320,9 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;
-        const int h = (warp - 2) >> 2;
-        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        const int h = (warp - kEpilogueWarp0) >> 2;
+        const float alpha = alpha_value(p.alpha);
+        const bool scale_by_alpha = alpha_enabled(p.alpha);
         int g = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -366,7 +363,7 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
             for (int i = 0; i < kBN / 2; ++i) {
                 float v = c[i];
                 if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
-                if (p.alpha) v = __fmul_rn(v, alpha);
+                if (scale_by_alpha) v = __fmul_rn(v, alpha);
                 c[i] = v;
             }
             if (p.bias) {
@@ -390,44 +387,10 @@ gemm_fallback_kernel(const __grid_constant__ CUtensorMap map_a_compact,
     // common exit: every role's loop is bounded, so all threads arrive here
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-}
-
-static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult query;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
-            query != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-    }
-    return fn;
-}
-
-// [rows, K] bf16 row-major -> 2-D tiled map with a (64 x box_rows) box, 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, uint32_t box_rows) {
-    PFN_cuTensorMapEncodeTiled_v12000 encode = encode_fn();
-    if (!encode) {
-        record_error_text("cuTensorMapEncodeTiled is not available from the driver");
-        return UE5M3_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
-    cuuint32_t elem_strides[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        record_error_text("cuTensorMapEncodeTiled failed for a decoded operand");
-        return UE5M3_ERR_CUDA;
-    }
-    return UE5M3_OK;
 }
 
 }  // namespace fb
@@ -435,18 +398,13 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K,
 
 using namespace ue5m3;
 
-extern "C" size_t ue5m3_gemm_fp4_fallback_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
-    return (size_t)(M + N + 2 * (int64_t)kRecMaxRows) * (size_t)K * 2;
-}
-
 extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_sf_raw, const int* a_record,
                                        const uint8_t* b_codes, const uint8_t* b_sf_raw, const int* b_record,
                                        int64_t M, int64_t N, int64_t K, int snap, const float* alpha_dev,
+                                       const float* amax_a_dev, const float* amax_b_dev, float inv_denominator,
                                        const void* bias, int bias_dtype, void* out, int out_dtype, int64_t ldo,
-                                       void* workspace, size_t workspace_bytes, int* status_dev, void* stream_v) {
-    if (!a_codes || !a_sf_raw || !a_record || !b_codes || !b_sf_raw || !b_record || !out || !workspace ||
-        M <= 0 || N <= 0 || K <= 0)
+                                       int* status_dev, void* stream_v) {
+    if (!a_codes || !a_sf_raw || !a_record || !b_codes || !b_sf_raw || !b_record || !out || M <= 0 || N <= 0 || K <= 0)
         return UE5M3_ERR_INVALID_ARGUMENT;
     if (K % fb::kBK) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if (out_dtype != UE5M3_DTYPE_BF16 && out_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
@@ -454,39 +412,25 @@ extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_
     if (ldo < N) return UE5M3_ERR_INVALID_ARGUMENT;
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
     if (((M + 127) / 128) * ((N + 255) / 256) > 0x3FFFFFFF) return UE5M3_ERR_TOO_LARGE;
-    if (((uintptr_t)workspace % 16) || ((uintptr_t)a_codes % 4) || ((uintptr_t)b_codes % 4) || (K / 2) % 4)
-        return UE5M3_ERR_ALIGNMENT;
-    if (workspace_bytes < ue5m3_gemm_fp4_fallback_workspace_bytes(M, N, K)) return UE5M3_ERR_SCRATCH;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-
-    __nv_bfloat16* ws = static_cast<__nv_bfloat16*>(workspace);
-    fb::DecodeArgs d;
-    d.codes[0] = a_codes; d.codes[1] = b_codes;
-    d.raw[0] = a_sf_raw; d.raw[1] = b_sf_raw;
-    d.rec[0] = a_record; d.rec[1] = b_record;
-    d.rows[0] = (int)M; d.rows[1] = (int)N; d.K = (int)K;
-    d.compact[0] = ws;
-    d.compact[1] = d.compact[0] + (size_t)kRecMaxRows * K;
-    d.full[0] = d.compact[1] + (size_t)kRecMaxRows * K;
-    d.full[1] = d.full[0] + (size_t)M * K;
-    fb::decode_operands_kernel<<<sm_count() * 8, 256, 0, stream>>>(d);
-    int status = check_launch();
-    if (status != UE5M3_OK) return status;
-
-    CUtensorMap map_ac, map_bf, map_af, map_bc;
-    if ((status = fb::make_map(&map_ac, d.compact[0], kRecMaxRows, K, fb::kBM)) != UE5M3_OK) return status;
-    if ((status = fb::make_map(&map_bf, d.full[1], N, K, fb::kBN)) != UE5M3_OK) return status;
-    if ((status = fb::make_map(&map_af, d.full[0], M, K, fb::kBM)) != UE5M3_OK) return status;
-    if ((status = fb::make_map(&map_bc, d.compact[1], kRecMaxRows, K, fb::kBN)) != UE5M3_OK) return status;
+    if (((uintptr_t)a_codes % 4) || ((uintptr_t)b_codes % 4)) return UE5M3_ERR_ALIGNMENT;
 
     fb::Params p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
-    p.alpha = alpha_dev; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.alpha = AlphaSpec{alpha_dev, amax_a_dev, amax_b_dev, inv_denominator};
+    if (!alpha_spec_valid(p.alpha)) return UE5M3_ERR_INVALID_ARGUMENT;
+    p.bias = bias; p.bias_dtype = bias_dtype;
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
+    p.codes_a = a_codes; p.codes_b = b_codes; p.raw_a = a_sf_raw; p.raw_b = b_sf_raw;
     p.rec_a = a_record; p.rec_b = b_record;
     const size_t smem = (size_t)fb::kStages * fb::kStageBytes + sizeof(fb::Barriers) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(fb::gemm_fallback_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return record_cuda_error(e);
-    fb::gemm_fallback_kernel<<<sm_count(), fb::kThreads, smem, stream>>>(map_ac, map_bf, map_af, map_bc, p);
+    static bool configured[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64 || !configured[device]) {
+        cudaError_t e = cudaFuncSetAttribute(fb::gemm_fallback_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (device >= 0 && device < 64) configured[device] = true;
+    }
+    fb::gemm_fallback_kernel<<<sm_count(), fb::kThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(p);
     return check_launch();
 }

@@ -27,6 +27,7 @@
 #include <stdint.h>
 
 #include "abi_common.cuh"
+#include "alpha_spec.cuh"
 #include "tcgen05_ptx.cuh"
 #include "window_record.cuh"
 
@@ -58,7 +59,7 @@ struct Fp4Params {
     int M, N, K;
     int snap;
     float rescale;  // 2^(shift_a + shift_b)
-    const float* alpha;
+    AlphaSpec alpha;
     const void* bias;
     int bias_dtype;
     void* out;
@@ -119,7 +120,7 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
         for (int i = 0; i < 32; ++i) {
             float x = __fmul_rn(__uint_as_float(v[chunk][i]), p.rescale);
             if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
-            if (p.alpha) x = __fmul_rn(x, alpha);
+            if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
             c[i] = x;
         }
         if (p.bias) {
@@ -192,7 +193,7 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, c
                 const int idx = pass * 64 + c * 8 + e;
                 float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), p.rescale);
                 if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
-                if (p.alpha) x = __fmul_rn(x, alpha);
+                if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
                 if (p.bias) {
                     const int col = col0 + c * 8 + e;
                     const float bv = p.bias_dtype == UE5M3_DTYPE_BF16
@@ -407,7 +408,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ---------------- epilogue: TMEM -> registers (release) -> arithmetic -> global ----------------
         const int q = warp & 3;          // TMEM lane quadrant
         const int h = (warp - 2) >> 2;   // column half of the tile
-        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        const float alpha = alpha_value(p.alpha);
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             int tile_m, tile_n;
@@ -703,7 +704,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // ---------------- epilogue (both CTAs): own 128 accumulator rows ----------------
         const int q = warp & 3;
         const int h = (warp - 2) >> 2;
-        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        const float alpha = alpha_value(p.alpha);
         const uint32_t tmem_empty_leader = map_to_cta(smem_u32(&bars->tmem_empty), 0);
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
@@ -892,14 +893,17 @@ extern "C" int ue5m3_pack_scales_ue4m3(const uint8_t* scales, int64_t rows, int6
 
 extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const uint8_t* b_codes,
                               const uint8_t* b_sf, int64_t M, int64_t N, int64_t K, int shift_sum,
-                              int snap, const float* alpha_dev, const void* bias, int bias_dtype,
-                              void* out, int out_dtype, int64_t ldo, int* status_dev, void* stream_v) {
+                              int snap, const float* alpha_dev, const float* amax_a_dev,
+                              const float* amax_b_dev, float inv_denominator, const void* bias,
+                              int bias_dtype, void* out, int out_dtype, int64_t ldo, int* status_dev,
+                              void* stream_v) {
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out || M <= 0 || N <= 0 || K <= 0)
         return UE5M3_ERR_INVALID_ARGUMENT;
     if (K % kFKMma) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if (out_dtype != UE5M3_DTYPE_BF16 && out_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (bias && bias_dtype != UE5M3_DTYPE_BF16 && bias_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (ldo < N || shift_sum < -100 || shift_sum > 100) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!alpha_spec_valid(AlphaSpec{alpha_dev, amax_a_dev, amax_b_dev, inv_denominator})) return UE5M3_ERR_INVALID_ARGUMENT;
     if (((uintptr_t)a_codes % 16) || ((uintptr_t)b_codes % 16) || ((uintptr_t)a_sf % 16) || ((uintptr_t)b_sf % 16))
         return UE5M3_ERR_ALIGNMENT;
     if (((K / 2) % 16) != 0) return UE5M3_ERR_ALIGNMENT;  // TMA row pitch
@@ -918,7 +922,8 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
     Fp4Params p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
     p.rescale = ldexpf(1.0f, shift_sum);
-    p.alpha = alpha_dev; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.alpha = AlphaSpec{alpha_dev, amax_a_dev, amax_b_dev, inv_denominator};
+    p.bias = bias; p.bias_dtype = bias_dtype;
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
     p.sfa = a_sf; p.sfb = b_sf;
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;

@@ -27,6 +27,7 @@
 #include <stdint.h>
 
 #include "abi_common.cuh"
+#include "alpha_spec.cuh"
 
 namespace ue5m3 {
 
@@ -46,7 +47,7 @@ constexpr long long kWaitBudgetClocks = 4000000000LL;  // about two seconds
 struct GemmParams {
     int M, N, K;
     int snap;
-    const float* alpha;
+    AlphaSpec alpha;
     const void* bias;
     int bias_dtype;
     void* out;
@@ -353,7 +354,8 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
             if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
         }
         if (ok) {
-            const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+            const float alpha = alpha_value(p.alpha);
+            const bool scale_by_alpha = alpha_enabled(p.alpha);
             const long long row = (long long)m0 + q * 32 + lane;
             const int col0 = n0 + h * (kBN / 2);
             if (row < p.M) {
@@ -361,7 +363,7 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
                 for (int i = 0; i < kBN / 2; ++i) {
                     float v = c[i];
                     if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
-                    if (p.alpha) v = __fmul_rn(v, alpha);
+                    if (scale_by_alpha) v = __fmul_rn(v, alpha);
                     c[i] = v;
                 }
                 if (p.bias) {
@@ -469,13 +471,16 @@ using namespace ue5m3;
 
 extern "C" int ue5m3_gemm_issue_rz_bf16(const void* a, const void* bt, int64_t M, int64_t N,
                                         int64_t K, int snap, const float* alpha_dev,
-                                        const void* bias, int bias_dtype, void* out, int out_dtype,
-                                        int64_t ldo, int* status_dev, void* stream_v) {
+                                        const float* amax_a_dev, const float* amax_b_dev,
+                                        float inv_denominator, const void* bias, int bias_dtype,
+                                        void* out, int out_dtype, int64_t ldo, int* status_dev,
+                                        void* stream_v) {
     if (!a || !bt || !out || M <= 0 || N <= 0 || K <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
     if (K % kBK) return UE5M3_ERR_K_NOT_DIVISIBLE;
     if (out_dtype != UE5M3_DTYPE_BF16 && out_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (bias && bias_dtype != UE5M3_DTYPE_BF16 && bias_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (ldo < N) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!alpha_spec_valid(AlphaSpec{alpha_dev, amax_a_dev, amax_b_dev, inv_denominator})) return UE5M3_ERR_INVALID_ARGUMENT;
     if (((uintptr_t)a % 16) || ((uintptr_t)bt % 16)) return UE5M3_ERR_ALIGNMENT;
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
     const int64_t tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + kBN - 1) / kBN;
@@ -489,7 +494,8 @@ extern "C" int ue5m3_gemm_issue_rz_bf16(const void* a, const void* bt, int64_t M
 
     GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
-    p.alpha = alpha_dev; p.bias = bias; p.bias_dtype = bias_dtype;
+    p.alpha = AlphaSpec{alpha_dev, amax_a_dev, amax_b_dev, inv_denominator};
+    p.bias = bias; p.bias_dtype = bias_dtype;
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
 

@@ -71,7 +71,7 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_alpha.restype = i32
     lib.ue5m3_alpha.argtypes = [p, p, f32, p, p]
     lib.ue5m3_gemm_issue_rz_bf16.restype = i32
-    lib.ue5m3_gemm_issue_rz_bf16.argtypes = [p, p, i64, i64, i64, i32, p, p, i32, p, i32, i64, p, p]
+    lib.ue5m3_gemm_issue_rz_bf16.argtypes = [p, p, i64, i64, i64, i32, p, p, p, f32, p, i32, p, i32, i64, p, p]
     lib.ue5m3_packed_scales_bytes.restype = sz
     lib.ue5m3_packed_scales_bytes.argtypes = [i64, i64]
     lib.ue5m3_pack_scales_ue4m3.restype = i32
@@ -86,14 +86,12 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_rht_amax_t.argtypes = [p, i32, i64, i64, p, p]
     lib.ue5m3_quantize_fp4_operand_t_rht.restype = i32
     lib.ue5m3_quantize_fp4_operand_t_rht.argtypes = [p, i32, i64, i64, p, f32, i32, p, i32, i32, p, p, p, p, p]
-    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.restype = sz
-    lib.ue5m3_gemm_fp4_fallback_workspace_bytes.argtypes = [i64, i64, i64]
     lib.ue5m3_gemm_fp4_fallback.restype = i32
-    lib.ue5m3_gemm_fp4_fallback.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, p, p, i32, p, i32, i64, p, sz, p, p]
+    lib.ue5m3_gemm_fp4_fallback.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, p, p, p, f32, p, i32, p, i32, i64, p, p]
     lib.ue5m3_philox_bytes.restype = i32
     lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
-    lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, i32, p, i32, i64, p, p]
+    lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, p, f32, p, i32, p, i32, i64, p, p]
     lib.ue5m3_test_e2m1_cvt.restype = i32
     lib.ue5m3_test_e2m1_cvt.argtypes = [ctypes.c_uint32, ctypes.c_uint64, p, p, p]
     if hasattr(lib, "ue5m3_amax_static"):

@@ -279,6 +279,40 @@ def dequantize_packed(
     return out
 
 
+@dataclass(slots=True)
+class EpilogueAlpha:
+    """alpha of a GEMM epilogue given by its ingredients: the two held tensor amaxes (device
+    scalars) and the fp32 reciprocal of (Ta*6)*(Tb*6).  The kernels form
+    fl(fl(amax_a*amax_b) * inv_denominator) themselves, which is the value
+    ``encoded_global_alpha`` computes with two ATen launches."""
+
+    amax_a: Tensor
+    amax_b: Tensor
+    inv_denominator: float
+
+    @classmethod
+    def of(cls, amax_a: Tensor, amax_b: Tensor, target_a: float, target_b: float) -> "EpilogueAlpha":
+        import numpy as np
+
+        denominator = np.float32((float(target_a) * 6.0) * (float(target_b) * 6.0))
+        return cls(amax_a.reshape(1), amax_b.reshape(1), float(np.float32(1.0) / denominator))
+
+
+def _alpha_arguments(alpha, device: torch.device) -> tuple:
+    """(alpha_dev, amax_a_dev, amax_b_dev, inv_denominator) of the C ABI."""
+
+    if alpha is None:
+        return (None, None, None, 0.0)
+    if isinstance(alpha, EpilogueAlpha):
+        for value in (alpha.amax_a, alpha.amax_b):
+            if value.dtype is not torch.float32 or value.numel() != 1 or value.device != device:
+                raise ValueError("tensor amaxes must be one-element float32 tensors on the operands' device")
+        return (None, alpha.amax_a.data_ptr(), alpha.amax_b.data_ptr(), alpha.inv_denominator)
+    if alpha.dtype is not torch.float32 or alpha.numel() != 1 or alpha.device != device:
+        raise ValueError("alpha must be a one-element float32 tensor on the operands' device")
+    return (alpha.data_ptr(), None, None, 0.0)
+
+
 _status_words: dict[torch.device, Tensor] = {}
 
 
@@ -335,7 +369,7 @@ def gemm_issue_rz(
     bt: Tensor,
     *,
     snap: bool,
-    alpha: Tensor | None = None,
+    alpha: "Tensor | EpilogueAlpha | None" = None,
     bias: Tensor | None = None,
     out_dtype: torch.dtype = torch.float32,
 ) -> Tensor:
@@ -356,14 +390,13 @@ def gemm_issue_rz(
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if m == 0 or n == 0:
         return out
-    if alpha is not None and (alpha.dtype is not torch.float32 or alpha.numel() != 1 or alpha.device != a.device):
-        raise ValueError("alpha must be a one-element float32 tensor on the operands' device")
+    alpha_args = _alpha_arguments(alpha, a.device)
     if bias is not None:
         if bias.numel() != n or bias.device != a.device or not bias.is_contiguous():
             raise ValueError("bias must be a contiguous vector of length N on the operands' device")
     with torch.cuda.device(a.device):
         status = _native.load().ue5m3_gemm_issue_rz_bf16(
-            a.data_ptr(), bt.data_ptr(), m, n, k, int(bool(snap)), _native.ptr(alpha),
+            a.data_ptr(), bt.data_ptr(), m, n, k, int(bool(snap)), *alpha_args,
             _native.ptr(bias), _native.dtype_code(bias.dtype) if bias is not None else 0,
             out.data_ptr(), _native.dtype_code(out_dtype), n, gemm_status(a.device).data_ptr(),
             _native.stream_ptr(a.device),
@@ -414,7 +447,8 @@ def pack_scales(scales: Tensor, *, rows: int, k: int, block_size: int, two_dimen
 
 def gemm_fp4(
     a_codes: Tensor, a_sf: Tensor, b_codes: Tensor, b_sf: Tensor, *, m: int, n: int, k: int, shift_sum: int,
-    snap: bool, alpha: Tensor | None = None, bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32,
+    snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None, bias: Tensor | None = None,
+    out_dtype: torch.dtype = torch.float32,
 ) -> Tensor:
     """out[M,N] on packed E2M1 codes + packed scales with the FP4 block-scaled tensor cores."""
 
@@ -427,7 +461,7 @@ def gemm_fp4(
     with torch.cuda.device(a_codes.device):
         status = _native.load().ue5m3_gemm_fp4(
             a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(), m, n, k, shift_sum,
-            int(bool(snap)), _native.ptr(alpha), _native.ptr(bias),
+            int(bool(snap)), *_alpha_arguments(alpha, a_codes.device), _native.ptr(bias),
             _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
             _native.dtype_code(out_dtype), n, gemm_status(a_codes.device).data_ptr(),
             _native.stream_ptr(a_codes.device),
@@ -602,7 +636,7 @@ def hadamard_amax_transposed(x: Tensor) -> Tensor:
     return out
 
 
-def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor | None = None,
+def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None,
                       bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
     """FP4 tensor-core product of two packed operands, followed (stream-ordered, no host
     synchronisation) by the recomputation of whatever their window records list: output rows
@@ -617,19 +651,16 @@ def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: Tensor
                    shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype)
     if a.record is None or b.record is None or a.raw_scale_factors is None or b.raw_scale_factors is None:
         raise ValueError("packed operands must carry their raw scales and window records")
-    lib = _native.load()
-    workspace = torch.empty(lib.ue5m3_gemm_fp4_fallback_workspace_bytes(a.rows, b.rows, a.k),
-                            dtype=torch.uint8, device=out.device)
     with torch.cuda.device(out.device):
-        status = lib.ue5m3_gemm_fp4_fallback(
+        status = _native.load().ue5m3_gemm_fp4_fallback(
             a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(),
             b.codes.data_ptr(), b.raw_scale_factors.data_ptr(), b.record.data_ptr(),
-            a.rows, b.rows, a.k, int(bool(snap)), _native.ptr(alpha), _native.ptr(bias),
+            a.rows, b.rows, a.k, int(bool(snap)), *_alpha_arguments(alpha, out.device), _native.ptr(bias),
             _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
-            _native.dtype_code(out_dtype), b.rows, workspace.data_ptr(), workspace.numel(),
-            gemm_status(out.device).data_ptr(), _native.stream_ptr(out.device),
+            _native.dtype_code(out_dtype), b.rows, gemm_status(out.device).data_ptr(),
+            _native.stream_ptr(out.device),
         )
-    _native.check(status, "ue5m3_gemm_fp4_fallback", launches=2)
+    _native.check(status, "ue5m3_gemm_fp4_fallback")
     return out
 
 
@@ -877,6 +908,7 @@ __all__ = [
     "BLOCK_2D",
     "BLOCK_COL",
     "BLOCK_ROW",
+    "EpilogueAlpha",
     "Fp4Operand",
     "PackedOperand",
     "available",

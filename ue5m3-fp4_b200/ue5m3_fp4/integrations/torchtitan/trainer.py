@@ -27,17 +27,32 @@ def training_scale_states(model_parts: Iterable[nn.Module]) -> tuple[TrainingSca
 
 
 def begin_training_step(model_parts: Iterable[nn.Module], step: int) -> int:
-    """Advance every distinct scale state to `step`; models without FP4 linears are a no-op."""
+    """Advance every distinct scale state to `step`; models without FP4 linears are a no-op.
+
+    On a step at which weight references are due (1, 51, 101, ... with D = 50) the amaxes of
+    all FP4 linears' weights that share a state are then sampled together - they do not depend
+    on the step's activations - and reduced across the data-parallel ranks with ONE collective
+    (``TrainingScaleState.sample_weights``) instead of one per linear inside the forward pass."""
 
     if type(step) is not int or step < 1:
         raise ValueError("step must be a positive integer")
-    states = training_scale_states(model_parts)
+    parts = list(model_parts)
+    states = training_scale_states(parts)
     for state in states:
         if state.step is not None and state.step >= step:
             raise RuntimeError(
                 f"TorchTitan UE5M3 step hook was called out of order: state={state.step}, trainer={step}"
             )
         state.begin_step(step)
+    weights: dict[int, list] = {}
+    for part in parts:
+        for module in part.modules():
+            state = getattr(module, "scale_state", None)
+            name, weight = getattr(module, "module_name", None), getattr(module, "weight", None)
+            if isinstance(state, TrainingScaleState) and isinstance(name, str) and weight is not None and weight.is_cuda:
+                weights.setdefault(id(state), []).append((name, weight.detach()))
+    for state in states:
+        state.sample_weights(weights.get(id(state), ()))
     return len(states)
 
 

@@ -230,12 +230,15 @@ def _gemm(
 ) -> torch.Tensor:
     from ue5m3_fp4.backends import b200
 
-    alpha = b200.encoded_global_alpha(reference_a.reshape(1), reference_b.reshape(1), target_a, target_b)
+    # alpha = fl(fl(amax_a*amax_b) / ((Ta*6)*(Tb*6))) is formed inside the GEMM epilogue from the
+    # two held amaxes (no launch of its own)
+    alpha = b200.EpilogueAlpha.of(reference_a, reference_b, target_a, target_b)
     if isinstance(a_enc, b200.Fp4Operand):
         return b200.gemm_fp4_operands(a_enc, bt_enc, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
     if owner.backend is LinearBackend.PROBE_MATCHED_TRITON:
         return b200.gemm_issue_rz(a_enc, bt_enc, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
     # torch control: same encoded operands, library FP32 matrix multiplication
+    alpha = b200.encoded_global_alpha(reference_a.reshape(1), reference_b.reshape(1), target_a, target_b)
     with torch.autocast(device_type="cuda", enabled=False):
         out = torch.mm(a_enc.float(), bt_enc.float().t()) * alpha
     if bias is not None:
@@ -380,7 +383,8 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         )
         grad_bias = None
         if ctx.has_bias:
-            grad_bias = dy.to(torch.float32).sum(dim=0).to(ctx.bias_dtype)
+            # fp32 accumulation straight from the bf16 rows: no fp32 copy of dY is materialised
+            grad_bias = dy.sum(dim=0, dtype=torch.float32).to(ctx.bias_dtype)
         return grad_input.reshape(ctx.input_shape), grad_weight, grad_bias, None
 
 
