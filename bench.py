@@ -608,6 +608,11 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         conversion.scale_state.verify_samples()
         from ue5m3_fp4.backends import b200
 
+        b200.log_window_records(True)   # one more step, untimed: how much of it the recomputation pass took over
+        step(61)
+        torch.cuda.synchronize(device)
+        window = b200.window_log_summary()
+        b200.log_window_records(False)
         b200.check_gemm_status(device)
         peak_memory = torch.cuda.max_memory_allocated(device)
         torch.backends.cuda.matmul.allow_tf32 = previous_tf32
@@ -624,6 +629,7 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
             "amax_collectives_hold_step": 0,
             "fp4_linear_tflops_per_rank": model.fp4_linear_flops_per_token() * seq / (hold_ms * 1e-3) / 1e12,
             "parameters": parameters, "peak_memory_gb": peak_memory / 1e9, "n_gpus": world,
+            "scale_window": window,
         }
         del optimizer, wrapped, model
         torch.cuda.empty_cache()

@@ -12,14 +12,17 @@
 //   A x B over the whole output    -> when a list overflowed its capacity,
 // and per tile do what gemm_sm100.cu does: four K=16 BF16 MMAs into a fresh TMEM accumulator
 // per K=64 issue, round-toward-zero adds across issues in registers, then snap, alpha, bias,
-// cast.  The operands are not read as bf16 from memory: three producer warps decode the packed
+// cast.  The operands are not read as bf16 from memory: four producer warps decode the packed
 // E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
 // 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
-// the record.  No workspace, no separate decode pass.  The issue counter runs on across tiles,
+// the record (every thread looks its rows up once per tile and issues all the global loads of
+// a stage before it decodes any, so their latencies overlap).  No workspace,
+// no separate decode pass.  Tiles are 128 x 128: a listed-row pass has few tiles, and the
+// narrower tile spreads them over twice as many SMs.  The issue counter runs on across tiles,
 // so the mbarrier phases never need re-initialising.
 //
-// Warps: 0..2 producers, 3 MMA issuer and TMEM owner, 4..11 epilogue (TMEM lane quadrant =
-// warp % 4, column half = (warp - 4) / 4).  Every wait is clock-bounded.
+// Warps: 0..3 producers, 4 MMA issuer and TMEM owner, 5..12 epilogue (TMEM lane quadrant =
+// warp % 4, column half = (warp - 5) / 4).  Every wait is clock-bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -38,15 +41,15 @@ using namespace ptx;
 namespace fb {
 
 constexpr int kBM = 128;
-constexpr int kBN = 256;
+constexpr int kBN = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
-constexpr int kProducerWarps = 3;
+constexpr int kStages = 6;
+constexpr int kProducerWarps = 4;
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kEpilogueWarp0 = kMmaWarp + 1;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 32 * (kEpilogueWarp0 + kEpilogueWarps);
-constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemCols = 256;   // two 128-column accumulators
 constexpr uint32_t kStageBytesA = kBM * kBK * 2;
 constexpr uint32_t kStageBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
@@ -170,26 +173,39 @@ __device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-// One K=64 slab of `tile_rows` operand rows -> bf16 in the 128-byte-swizzled K-major layout:
-// row r occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk position c ^ (r & 7).
-// `first` = first local row, `count` = rows that exist (others become zero), `list` maps local
-// rows to operand rows (null: identity).
-__device__ __forceinline__ void produce_slab(unsigned char* smem_tile, int tile_rows, const uint8_t* __restrict__ codes,
-                                             const uint8_t* __restrict__ raw, const int* __restrict__ list, int first,
-                                             int count, int K, int issue, int producer_thread) {
-    const int64_t k_atoms = K / 64;
-    for (int item = producer_thread; item < tile_rows * 8; item += kProducerWarps * 32) {
-        const int r = item >> 3, c = item & 7;   // row of the tile, 8-element chunk of the issue
-        const int local = first + r;
-        uint4 value = make_uint4(0u, 0u, 0u, 0u);
-        if (local < count) {
-            const int64_t row = list ? (int64_t)__ldg(list + local) : local;
-            const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (K / 2) + issue * 32) + c);
-            const uint8_t byte = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 +
-                                       ((row >> 5) & 3) * 4 + (c >> 1));
-            value = decode_word(word, ue5m3_decode(byte));
+// One K=64 slab of the tile's A rows and B rows -> bf16 in the 128-byte-swizzled K-major
+// layout: row r of a tile occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk
+// position c ^ (r & 7).  An item is (row, 8-element chunk); every producer thread owns
+// kItems of them and issues all of their global loads before it decodes the first.
+constexpr int kItems = (kBM + kBN) * 8 / (kProducerWarps * 32);
+static_assert((kBM + kBN) * 8 % (kProducerWarps * 32) == 0, "items divide evenly over the producer threads");
+
+__device__ __forceinline__ void produce_stage(unsigned char* stage, const Params& p, const int (&item_row)[kItems],
+                                              int issue, int producer_thread) {
+    const int64_t k_atoms = p.K / 64;
+    uint32_t word[kItems];
+    uint32_t byte[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int item = producer_thread + i * (kProducerWarps * 32);
+        const int r = item >> 3, c = item & 7;        // r < kBM: A row, else B row
+        const int64_t row = item_row[i];   // operand row, -1 = beyond the operand
+        word[i] = 0u;
+        byte[i] = 0x78u;
+        if (row >= 0) {
+            const uint8_t* codes = r < kBM ? p.codes_a : p.codes_b;
+            const uint8_t* raw = r < kBM ? p.raw_a : p.raw_b;
+            word[i] = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (p.K / 2) + issue * 32) + c);
+            byte[i] = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (c >> 1));
         }
-        *reinterpret_cast<uint4*>(smem_tile + r * 128 + ((c ^ (r & 7)) << 4)) = value;
+    }
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int item = producer_thread + i * (kProducerWarps * 32);
+        const int r = item >> 3, c = item & 7;
+        const int local = r < kBM ? r : r - kBM;
+        unsigned char* tile = r < kBM ? stage : stage + kStageBytesA;
+        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) = decode_word(word[i], ue5m3_decode(byte[i]));
     }
 }
 
@@ -267,8 +283,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const Tile tile = locate_tile(plan, t, p.M, p.N);
-            const int* list_a = tile.job == 0 ? p.rec_a + kRecHeader : nullptr;
-            const int* list_b = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
+            // operand rows of this thread's items, looked up once per tile
+            int item_row[kItems];
+#pragma unroll
+            for (int i = 0; i < kItems; ++i) {
+                const int r = (threadIdx.x + i * (kProducerWarps * 32)) >> 3;
+                const bool is_a = r < kBM;
+                const int local = is_a ? tile.m0 + r : tile.n0 + (r - kBM);
+                const int count = is_a ? tile.rows : tile.cols;
+                item_row[i] = -1;
+                if (local < count) {
+                    if (is_a) item_row[i] = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
+                    else item_row[i] = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
+                }
+            }
             for (int j = 0; j < num_issues; ++j, ++g) {
                 const int s = g % kStages;
                 const uint32_t use = g / kStages;
@@ -277,9 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                 }
-                unsigned char* sa = smem + s * kStageBytes;
-                produce_slab(sa, kBM, p.codes_a, p.raw_a, list_a, tile.m0, tile.rows, p.K, j, threadIdx.x);
-                produce_slab(sa + kStageBytesA, kBN, p.codes_b, p.raw_b, list_b, tile.n0, tile.cols, p.K, j, threadIdx.x);
+                produce_stage(smem + s * kStageBytes, p, item_row, j, threadIdx.x);
                 fence_generic_to_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->full[s]);

@@ -636,6 +636,42 @@ def hadamard_amax_transposed(x: Tensor) -> Tensor:
     return out
 
 
+_window_log: list | None = None
+
+
+def log_window_records(enable: bool) -> None:
+    """Start (or stop and discard) keeping the window records of every FP4 product, for
+    ``window_log_summary``; diagnostic, off by default."""
+
+    global _window_log
+    _window_log = [] if enable else None
+
+
+def window_log_summary() -> dict:
+    """How many of the logged products had operand rows outside the scale window, and how the
+    recomputation pass ran for them; synchronises (one read for all records)."""
+
+    entries = _window_log or []
+    if not entries:
+        return {"products": 0}
+    heads = torch.stack([torch.stack((a[:2], b[:2])) for a, b, _ in entries]).tolist()
+    summary = {"products": len(entries), "with_listed_rows": 0, "with_listed_columns": 0, "recomputed_in_full": 0,
+               "listed_rows_total": 0, "listed_columns_total": 0, "recomputed_tflop": 0.0, "total_tflop": 0.0}
+    for ((rows_a, _), (rows_b, _)), (_, _, (m, n, k)) in zip(heads, entries):
+        flop = 2.0 * m * n * k / 1e12
+        summary["total_tflop"] += flop
+        if rows_a > FALLBACK_MAX_ROWS or rows_b > FALLBACK_MAX_ROWS:
+            summary["recomputed_in_full"] += 1
+            summary["recomputed_tflop"] += flop
+            continue
+        summary["with_listed_rows"] += rows_a > 0
+        summary["with_listed_columns"] += rows_b > 0
+        summary["listed_rows_total"] += rows_a
+        summary["listed_columns_total"] += rows_b
+        summary["recomputed_tflop"] += flop * min(1.0, rows_a / m + rows_b / n)
+    return summary
+
+
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None,
                       bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
     """FP4 tensor-core product of two packed operands, followed (stream-ordered, no host
@@ -661,6 +697,8 @@ def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tenso
             _native.stream_ptr(out.device),
         )
     _native.check(status, "ue5m3_gemm_fp4_fallback")
+    if _window_log is not None:
+        _window_log.append((a.record, b.record, (a.rows, b.rows, a.k)))
     return out
 
 
@@ -923,6 +961,8 @@ __all__ = [
     "pack_scales",
     "quantize_fp4_operand",
     "new_window_record",
+    "log_window_records",
+    "window_log_summary",
     "poll_gemm_status",
     "gemm_status",
     "issue_rz_bf16_gemm",
