@@ -659,6 +659,9 @@ def run_ours(args) -> None:
         raise SystemExit("the sm_100a library is not built: run python ue5m3-fp4_b200/build.py")
     peaks = _peaks()
     hot = HotPath(device, rank, world)
+    # UE5M3_BENCH_LEGS=c5,linear ... restricts the side legs while developing; the default runs all
+    chosen = {leg.strip() for leg in os.environ.get("UE5M3_BENCH_LEGS", "all").split(",")}
+    leg = lambda name: "all" in chosen or name in chosen  # noqa: E731
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -699,9 +702,10 @@ def run_ours(args) -> None:
     if rank == 0:
         clocks = sampler.summary()
         sustained_clocks = sampler.summary(sustained_begin, sustained_end)
-        quant = _quantize_headline(torch, b200, device, max(args.steps, 40), peaks)
-        quant["c1_round_trip"] = _round_trip_c1(torch, b200, device, 30, peaks)
-        cpu = cpu_baseline() if world == 1 else None
+        quant = _quantize_headline(torch, b200, device, max(args.steps, 40), peaks) if leg("quantize") else {}
+        if leg("quantize"):
+            quant["c1_round_trip"] = _round_trip_c1(torch, b200, device, 30, peaks)
+        cpu = cpu_baseline() if world == 1 and leg("cpu") else None
         # The FP4 kernel issues kind::mxf4nvf4 MMAs, four times the BF16 MMA rate of the same tensor
         # core; no FP4 peak is measured, so the denominators are 4 x the measured cuBLAS BF16
         # figures: the burst one for the in-step CUDA-event time of the short run, the sustained
@@ -712,7 +716,7 @@ def run_ours(args) -> None:
         achieved_sustained = flops_per_rank / gemm_sustained_s / 1e12
         gemm_kernel = ("gemm_fp4_pair_kernel" if os.environ.get("UE5M3_FP4_CTA_PAIR", "1") != "0" else "gemm_fp4_kernel") \
             if fp4 else "gemm_issue_rz_kernel"
-        library_tf = _library_fp4_reference(torch, device) if fp4 else None
+        library_tf = _library_fp4_reference(torch, device) if fp4 and leg("library") else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
@@ -764,7 +768,7 @@ def run_ours(args) -> None:
     # free the C3 buffers before the larger configurations
     del hot
     torch.cuda.empty_cache()
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and leg("linear"):
         line["linear_step"] = _linear_case(
             torch, device, tokens=M, in_f=K, out_f=N, block=16, name="layers.1.mixer.up_proj", activation="normal",
             dy_scale=1e-3, steps=10, what="UE5M3Linear forward + backward, up_proj: tokens 8192, in 4096, out 21504, B=16, X ~ N(0,1)")
@@ -780,7 +784,7 @@ def run_ours(args) -> None:
             what="full FP4 linear forward + backward, down_proj B=32: X 16384x21504 relu(z)^2, W 4096x21504, dY 16384x4096 "
                  "N(0,1e-4^2), StochasticFast on dY, target 2048 on dY for dW, hold step of the D=50 lifecycle")
         torch.cuda.empty_cache()
-    if os.environ.get("UE5M3_BENCH_C5", "1") != "0":
+    if leg("c5"):
         c5 = _c5_training_step(torch, dist, device, rank, world, local_rank)
         if rank == 0:
             line["c5"] = c5

@@ -161,14 +161,16 @@ __device__ __forceinline__ Tile locate_tile(const Plan& plan, int t, int M, int 
     return tile;
 }
 
-// eight codes (one 32-bit word) x one scale -> eight bf16 values
+// eight codes (one 32-bit word) x one scale -> eight bf16 values; per byte: the hardware
+// E2M1 -> f16 pair conversion, two exact fp32 products, one pack to a bf16 pair
 __device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
     uint32_t out[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float lo = __fmul_rn(e2m1_value((word >> (8 * i)) & 0xFu), scale);
-        const float hi = __fmul_rn(e2m1_value((word >> (8 * i + 4)) & 0xFu), scale);
-        out[i] = float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
+        float lo, hi;
+        e2m1_unpack2_hw((word >> (8 * i)) & 0xFFu, lo, hi);
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(__fmul_rn(lo, scale), __fmul_rn(hi, scale));
+        out[i] = *reinterpret_cast<const uint32_t*>(&pair);
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
@@ -180,32 +182,40 @@ __device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
 constexpr int kItems = (kBM + kBN) * 8 / (kProducerWarps * 32);
 static_assert((kBM + kBN) * 8 % (kProducerWarps * 32) == 0, "items divide evenly over the producer threads");
 
-__device__ __forceinline__ void produce_stage(unsigned char* stage, const Params& p, const int (&item_row)[kItems],
-                                              int issue, int producer_thread) {
-    const int64_t k_atoms = p.K / 64;
+struct StageLoads {
     uint32_t word[kItems];
     uint32_t byte[kItems];
+};
+
+// issues the global loads of one stage (they complete while the previous stage is decoded)
+__device__ __forceinline__ void load_stage(StageLoads& loads, const Params& p, const int (&item_row)[kItems], int issue,
+                                           int producer_thread) {
+    const int64_t k_atoms = p.K / 64;
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
         const int r = item >> 3, c = item & 7;        // r < kBM: A row, else B row
-        const int64_t row = item_row[i];   // operand row, -1 = beyond the operand
-        word[i] = 0u;
-        byte[i] = 0x78u;
+        const int64_t row = item_row[i];              // operand row, -1 = beyond the operand
+        loads.word[i] = 0u;
+        loads.byte[i] = 0x78u;
         if (row >= 0) {
             const uint8_t* codes = r < kBM ? p.codes_a : p.codes_b;
             const uint8_t* raw = r < kBM ? p.raw_a : p.raw_b;
-            word[i] = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (p.K / 2) + issue * 32) + c);
-            byte[i] = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (c >> 1));
+            loads.word[i] = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (p.K / 2) + issue * 32) + c);
+            loads.byte[i] = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (c >> 1));
         }
     }
+}
+
+__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, int producer_thread) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
         const int r = item >> 3, c = item & 7;
         const int local = r < kBM ? r : r - kBM;
         unsigned char* tile = r < kBM ? stage : stage + kStageBytesA;
-        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) = decode_word(word[i], ue5m3_decode(byte[i]));
+        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) =
+            decode_word(loads.word[i], ue5m3_decode(loads.byte[i]));
     }
 }
 
@@ -297,18 +307,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
                     else item_row[i] = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
                 }
             }
+            StageLoads current, next;
+            load_stage(current, p, item_row, 0, threadIdx.x);
             for (int j = 0; j < num_issues; ++j, ++g) {
                 const int s = g % kStages;
                 const uint32_t use = g / kStages;
+                if (j + 1 < num_issues) load_stage(next, p, item_row, j + 1, threadIdx.x);
                 if (use > 0) {
                     ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                 }
-                produce_stage(smem + s * kStageBytes, p, item_row, j, threadIdx.x);
+                store_stage(smem + s * kStageBytes, current, threadIdx.x);
                 fence_generic_to_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->full[s]);
+                current = next;
             }
         }
     } else if (warp == kMmaWarp) {

@@ -11,9 +11,9 @@ of a training step runs at its real size.
 
 What it is NOT: the mixers between the linears are cheap stand-ins, because the selective-scan
 and causal-conv kernels of Mamba2 are separate libraries that are not part of this package.
-The Mamba2 stand-in gates the two 8192-wide streams of ``in_proj`` (silu(z) * x) and folds the
-B, C and dt columns in as a per-token scalar so that every output column of ``in_proj`` receives
-a gradient; attention is torch's scaled-dot-product attention (causal, 32 query heads over 4
+The Mamba2 stand-in gates the two 8192-wide streams of ``in_proj`` (silu(z) * x) and adds the
+B, C and dt columns onto the first 2176 channels, so that every output column of ``in_proj``
+receives a gradient of the same order of magnitude; attention is torch's scaled-dot-product attention (causal, 32 query heads over 4
 key/value heads of width 128, the reported k/v width 512); the MLP is up_proj ->
 squared ReLU -> down_proj as in the model.  Outputs of this stack mean nothing; its cost profile
 (FLOPs in the 112 linears, bytes of weights and gradients, number of amax samples) is the
@@ -70,8 +70,9 @@ class _MambaStandIn(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         z, u, rest = self.in_proj(x).split((self.inner, self.inner, self.extra), dim=-1)
-        gate = torch.tanh(rest.float().mean(dim=-1, keepdim=True)).to(u.dtype)
-        return self.out_proj(F.silu(z) * u * (1 + gate))
+        mixed = F.silu(z) * u
+        mixed = torch.cat((mixed[..., :self.extra] + rest, mixed[..., self.extra:]), dim=-1)
+        return self.out_proj(mixed)
 
 
 class _Attention(nn.Module):
