@@ -188,7 +188,7 @@ int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N
  *   [4 + UE5M3_FALLBACK_MAX_ROWS .. + rows) one flag per operand row.
  * No reference counterpart (the reference has no packed operands and no scale window).
  */
-#define UE5M3_FALLBACK_MAX_ROWS 1024
+#define UE5M3_FALLBACK_MAX_ROWS 4096
 #define UE5M3_WINDOW_RECORD_HEADER 4
 size_t ue5m3_window_record_ints(int64_t operand_rows);
 

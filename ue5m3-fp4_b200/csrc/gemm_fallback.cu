@@ -12,7 +12,7 @@
 //   A x B over the whole output    -> when a list overflowed its capacity,
 // and per tile do what gemm_sm100.cu does: four K=16 BF16 MMAs into a fresh TMEM accumulator
 // per K=64 issue, round-toward-zero adds across issues in registers, then snap, alpha, bias,
-// cast.  The operands are not read as bf16 from memory: four producer warps decode the packed
+// cast.  The operands are not read as bf16 from memory: seven producer warps decode the packed
 // E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
 // 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
 // the record (every thread looks its rows up once per tile and issues all the global loads of
@@ -21,8 +21,8 @@
 // narrower tile spreads them over twice as many SMs.  The issue counter runs on across tiles,
 // so the mbarrier phases never need re-initialising.
 //
-// Warps: 0..3 producers, 4 MMA issuer and TMEM owner, 5..12 epilogue (TMEM lane quadrant =
-// warp % 4, column half = (warp - 5) / 4).  Every wait is clock-bounded.
+// Warps: 0..6 producers, 7 MMA issuer and TMEM owner, 8..15 epilogue (TMEM lane quadrant =
+// warp % 4, column half = (warp - 8) / 4).  Every wait is clock-bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -44,7 +44,7 @@ constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kBK = 64;
 constexpr int kStages = 6;
-constexpr int kProducerWarps = 4;
+constexpr int kProducerWarps = 7;   // 16 warps in all: register files are handed out per four warps
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kEpilogueWarp0 = kMmaWarp + 1;
 constexpr int kEpilogueWarps = 8;
@@ -98,6 +98,7 @@ struct __align__(8) Barriers {
     unsigned long long tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
+    uint32_t pair_lut[256];   // packed byte (two E2M1 codes) -> their two values as a bf16 pair
 };
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -161,16 +162,18 @@ __device__ __forceinline__ Tile locate_tile(const Plan& plan, int t, int M, int 
     return tile;
 }
 
-// eight codes (one 32-bit word) x one scale -> eight bf16 values; per byte: the hardware
-// E2M1 -> f16 pair conversion, two exact fp32 products, one pack to a bf16 pair
-__device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
+// eight codes (one 32-bit word) x one scale -> eight bf16 values: per byte one table lookup
+// (the two payload values as a bf16 pair) and one packed bf16 multiply by the scale, which is
+// exact (a 2-bit by a 4-bit significand)
+__device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale_byte, const uint32_t* pair_lut) {
+    const __nv_bfloat16 scale = __float2bfloat16_rn(ue5m3_decode(scale_byte));   // 4 significant bits: exact
+    const __nv_bfloat162 scale2 = __halves2bfloat162(scale, scale);
     uint32_t out[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float lo, hi;
-        e2m1_unpack2_hw((word >> (8 * i)) & 0xFFu, lo, hi);
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(__fmul_rn(lo, scale), __fmul_rn(hi, scale));
-        out[i] = *reinterpret_cast<const uint32_t*>(&pair);
+        const uint32_t bits = pair_lut[(word >> (8 * i)) & 0xFFu];
+        const __nv_bfloat162 product = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits), scale2);
+        out[i] = *reinterpret_cast<const uint32_t*>(&product);
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
@@ -179,8 +182,8 @@ __device__ __forceinline__ uint4 decode_word(uint32_t word, float scale) {
 // layout: row r of a tile occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk
 // position c ^ (r & 7).  An item is (row, 8-element chunk); every producer thread owns
 // kItems of them and issues all of their global loads before it decodes the first.
-constexpr int kItems = (kBM + kBN) * 8 / (kProducerWarps * 32);
-static_assert((kBM + kBN) * 8 % (kProducerWarps * 32) == 0, "items divide evenly over the producer threads");
+constexpr int kStageItems = (kBM + kBN) * 8;
+constexpr int kItems = (kStageItems + kProducerWarps * 32 - 1) / (kProducerWarps * 32);   // the last one may not exist
 
 struct StageLoads {
     uint32_t word[kItems];
@@ -195,7 +198,7 @@ __device__ __forceinline__ void load_stage(StageLoads& loads, const Params& p, c
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
         const int r = item >> 3, c = item & 7;        // r < kBM: A row, else B row
-        const int64_t row = item_row[i];              // operand row, -1 = beyond the operand
+        const int64_t row = item_row[i];              // operand row, -1 = beyond the operand (or no such item)
         loads.word[i] = 0u;
         loads.byte[i] = 0x78u;
         if (row >= 0) {
@@ -207,15 +210,17 @@ __device__ __forceinline__ void load_stage(StageLoads& loads, const Params& p, c
     }
 }
 
-__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, int producer_thread) {
+__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, const uint32_t* pair_lut,
+                                            int producer_thread) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
+        if (item >= kStageItems) break;
         const int r = item >> 3, c = item & 7;
         const int local = r < kBM ? r : r - kBM;
         unsigned char* tile = r < kBM ? stage : stage + kStageBytesA;
         *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) =
-            decode_word(loads.word[i], ue5m3_decode(loads.byte[i]));
+            decode_word(loads.word[i], loads.byte[i], pair_lut);
     }
 }
 
@@ -279,6 +284,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
         mbar_fence_init();
     }
     if (warp == kMmaWarp) tmem_alloc(&bars->tmem_base, kTmemCols);
+    if (threadIdx.x < 256) {
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(e2m1_value(threadIdx.x & 0xFu), e2m1_value(threadIdx.x >> 4));
+        bars->pair_lut[threadIdx.x] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -302,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
                 const int local = is_a ? tile.m0 + r : tile.n0 + (r - kBM);
                 const int count = is_a ? tile.rows : tile.cols;
                 item_row[i] = -1;
-                if (local < count) {
+                if (r < kBM + kBN && local < count) {
                     if (is_a) item_row[i] = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
                     else item_row[i] = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
                 }
@@ -318,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                 }
-                store_stage(smem + s * kStageBytes, current, threadIdx.x);
+                store_stage(smem + s * kStageBytes, current, bars->pair_lut, threadIdx.x);
                 fence_generic_to_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->full[s]);

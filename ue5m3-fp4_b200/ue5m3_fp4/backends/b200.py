@@ -405,7 +405,7 @@ def gemm_issue_rz(
     return out
 
 
-FALLBACK_MAX_ROWS = 1024  # UE5M3_FALLBACK_MAX_ROWS of the C ABI
+FALLBACK_MAX_ROWS = 4096  # UE5M3_FALLBACK_MAX_ROWS of the C ABI
 
 
 def new_window_record(rows: int, device: torch.device) -> Tensor:
@@ -656,14 +656,20 @@ def window_log_summary() -> dict:
         return {"products": 0}
     heads = torch.stack([torch.stack((a[:2], b[:2])) for a, b, _ in entries]).tolist()
     summary = {"products": len(entries), "with_listed_rows": 0, "with_listed_columns": 0, "recomputed_in_full": 0,
-               "listed_rows_total": 0, "listed_columns_total": 0, "recomputed_tflop": 0.0, "total_tflop": 0.0}
+               "listed_rows_total": 0, "listed_columns_total": 0, "recomputed_tflop": 0.0, "total_tflop": 0.0,
+               "in_full_by_shape": {}, "listed_by_shape": {}}
     for ((rows_a, _), (rows_b, _)), (_, _, (m, n, k)) in zip(heads, entries):
         flop = 2.0 * m * n * k / 1e12
         summary["total_tflop"] += flop
+        shape = f"{m}x{n}x{k}"
         if rows_a > FALLBACK_MAX_ROWS or rows_b > FALLBACK_MAX_ROWS:
             summary["recomputed_in_full"] += 1
             summary["recomputed_tflop"] += flop
+            key = f"{shape}:{'A' if rows_a > FALLBACK_MAX_ROWS else ''}{'B' if rows_b > FALLBACK_MAX_ROWS else ''}"
+            summary["in_full_by_shape"][key] = summary["in_full_by_shape"].get(key, 0) + 1
             continue
+        if rows_a or rows_b:
+            summary["listed_by_shape"][shape] = summary["listed_by_shape"].get(shape, 0) + 1
         summary["with_listed_rows"] += rows_a > 0
         summary["with_listed_columns"] += rows_b > 0
         summary["listed_rows_total"] += rows_a
