@@ -568,12 +568,15 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         if world > 1:
             wrapped = DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True,
                                               bucket_cap_mb=200, broadcast_buffers=False)
-        optimizer = torch.optim.AdamW(model.parameters(), lr=1e-5, fused=True)
+        # learning rate 0: the optimizer step runs in full (same kernels, same memory traffic) but the
+        # weights keep the statistics of their random initialisation, so that the synthetic
+        # activations and gradients do not drift toward whatever a repeated random batch rewards
+        optimizer = torch.optim.AdamW(model.parameters(), lr=0.0, fused=True)
         g = torch.Generator(device=device).manual_seed(100 + rank)
-        ids = torch.randint(0, model.config.vocab_size, (1, seq), device=device, generator=g)
-        labels = torch.roll(ids, -1, dims=1).reshape(-1)
 
         def step(index: int, sync: bool = True) -> None:
+            ids = torch.randint(0, model.config.vocab_size, (1, seq), device=device, generator=g)  # fresh batch
+            labels = torch.roll(ids, -1, dims=1).reshape(-1)
             begin_training_step([model], index)
             context = nullcontext() if (sync or world == 1) else wrapped.no_sync()
             with context:
@@ -618,8 +621,9 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         torch.backends.cuda.matmul.allow_tf32 = previous_tf32
         result = {
             "what": "Nemotron-H-8B-shaped stack (52 layers, 112 FP4 linears B=16 at their real shapes, stand-in mixers, "
-                    "FP32 head with TF32 matmul), seq 8192, micro-batch 1 per GPU, forward + backward + fused AdamW "
-                    "(bf16 parameters and optimizer state), torch DDP, bf16 gradient buckets of 200 MB",
+                    "FP32 head with TF32 matmul), uniform random token ids drawn per step, seq 8192, micro-batch 1 per GPU, "
+                    "forward + backward + fused AdamW (bf16 parameters and optimizer state, learning rate 0), torch DDP, "
+                    "bf16 gradient buckets of 200 MB",
             "tokens_per_s": seq * world / (hold_ms * 1e-3), "ms_hold_step": hold_ms, "ms_refresh_step": refresh_ms,
             "tokens_per_s_refresh_step": seq * world / (refresh_ms * 1e-3),
             "ms_hold_step_without_gradient_allreduce": local_ms,
