@@ -175,22 +175,39 @@ int ue5m3_gemm_issue_rz_bf16(const void *a, const void *bt, int64_t M, int64_t N
 
 /*
  * Window record of one packed GEMM operand.  The FP4 tensor core takes UE4M3 block scales
- * (15 binades); UE5M3 spans 32 (formats.py:125-134), so after the per-tensor re-bias a block
- * scale can fall outside.  Its byte is then clamped in the tensor-core scale atoms, and the
- * operand ROW that holds it is written into this record, so that ue5m3_gemm_fp4_fallback can
- * recompute the output rows (A operand) or columns (B operand) it touches.  Layout (int32,
- * zero-filled by the caller before the operand is quantized):
- *   [0] number of distinct rows listed (a value > UE5M3_FALLBACK_MAX_ROWS means the list
- *       overflowed and the whole product is recomputed),
- *   [1] number of 16-element units whose scale was outside the window (diagnostic),
- *   [2], [3] reserved,
- *   [4 .. 4 + UE5M3_FALLBACK_MAX_ROWS) the listed rows, in no particular order,
- *   [4 + UE5M3_FALLBACK_MAX_ROWS .. + rows) one flag per operand row.
+ * (15 binades); UE5M3 spans 32 (formats.py:125-134).  The quantizers re-bias all scales of a
+ * tensor by one power of two (`shift`); a block scale that then falls outside UE4M3's normal
+ * range is clamped in the tensor-core scale atoms and its operand ROW is flagged here.
+ * ue5m3_place_row_windows afterwards gives every flagged row whose own scales fit 15 binades a
+ * shift of its own (exact: the GEMM epilogue multiplies the affected output rows / columns by
+ * the matching power of two) and lists the rows that still do not fit, for
+ * ue5m3_gemm_fp4_fallback to recompute.  Layout (int32, zero-filled by the caller before the
+ * operand is quantized), R = operand rows:
+ *   [0] distinct rows flagged by the quantizer
+ *   [1] 16-element units whose scale was outside the window at the tensor's shift (diagnostic)
+ *   [2] rows listed for recomputation (a value > UE5M3_FALLBACK_MAX_ROWS means the list
+ *       overflowed and the whole product is recomputed)
+ *   [3] rows that got a shift of their own
+ *   [4 .. 4 + UE5M3_FALLBACK_MAX_ROWS)      the listed rows, in no particular order
+ *   [.. + R)                                one flag per operand row
+ *   [.. + R)                                per row: its shift minus the tensor's shift (0 if unplaced)
  * No reference counterpart (the reference has no packed operands and no scale window).
  */
 #define UE5M3_FALLBACK_MAX_ROWS 4096
 #define UE5M3_WINDOW_RECORD_HEADER 4
 size_t ue5m3_window_record_ints(int64_t operand_rows);
+
+/*
+ * Row-wise placement of the scale window for the two operands of one product (either record
+ * may be NULL): rewrites the UE4M3 atoms of flagged rows that fit a window of their own,
+ * stores their extra exponents in the record and lists the others.  One launch; returns at
+ * once on the device when nothing is flagged.  a_shift / b_shift: the tensors' shifts as
+ * passed to the quantizers.  Call it between the quantizers and ue5m3_gemm_fp4.
+ * No reference counterpart.
+ */
+int ue5m3_place_row_windows(uint8_t *a_sf, const uint8_t *a_sf_raw, int *a_record, int64_t a_rows,
+                            int a_shift, uint8_t *b_sf, const uint8_t *b_sf_raw, int *b_record,
+                            int64_t b_rows, int b_shift, int64_t K, void *stream);
 
 /*
  * UE5M3 scale bytes -> the block-scaled tensor core's UE4M3 scale-factor layout.
@@ -199,8 +216,10 @@ size_t ue5m3_window_record_ints(int64_t operand_rows);
  * [ceil(rows/128)][K/64][512]; within a 512-byte atom the byte of row r0 + 32*r1 and 16-block
  * kb sits at r0*16 + r1*4 + kb.  Each byte is the UE5M3 byte minus ((8 + shift) << 3), i.e.
  * the same scale divided by 2^shift in UE4M3, clamped to UE4M3's normal range 0x08..0x7E when
- * it does not fit; such rows go into window_record (see above).  sf_raw (nullable, same size
- * and layout) receives the unmodified UE5M3 bytes, which the fallback decodes.
+ * it does not fit; such rows are flagged in window_record (see above).  sf_raw (nullable, same
+ * size and layout) receives the unmodified UE5M3 bytes, which the row placement and the
+ * recomputation pass read; the one-pass operand quantizers write 0 there for a block whose
+ * elements are all zero (its scale is immaterial).
  * No reference counterpart.
  */
 size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K);
@@ -261,19 +280,23 @@ int ue5m3_quantize_fp4_operand_t_rht(const void *x, int dtype, int64_t rows, int
  * a_codes [M, K/2], b_codes [N, K/2] (E2M1 nibbles, reduction axis contiguous); a_sf, b_sf from
  * ue5m3_pack_scales_ue4m3; shift_sum = shift_a + shift_b.  One MMA instruction per K=64 issue,
  * accumulated by the tensor core in FP32; epilogue as ue5m3_gemm_issue_rz_bf16 (snap, alpha,
- * bias, cast).  Replaces the same reference code as ue5m3_gemm_issue_rz_bf16
+ * bias, cast).  a_record / b_record (nullable): the operands' window records after
+ * ue5m3_place_row_windows; rows placed there are rescaled by their own power of two.
+ * Replaces the same reference code as ue5m3_gemm_issue_rz_bf16
  * (backends/triton/gemm.py:26-160, api.py:72-83).  K % 64 == 0, (K/2) % 16 == 0.
  */
 int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b_codes,
                    const uint8_t *b_sf, int64_t M, int64_t N, int64_t K, int shift_sum, int snap,
                    const float *alpha_dev, const float *amax_a_dev, const float *amax_b_dev,
                    float inv_denominator, const void *bias, int bias_dtype, void *out,
-                   int out_dtype, int64_t ldo, int *status_dev, void *stream);
+                   int out_dtype, int64_t ldo, const int *a_record, const int *b_record,
+                   int *status_dev, void *stream);
 
 /*
  * Second half of the FP4 product for operands whose window records are not empty: called
  * after ue5m3_gemm_fp4 on the same stream with the same epilogue arguments, it overwrites
- * the output rows listed in a_record and the output columns listed in b_record (everything,
+ * the output rows listed in a_record and the output columns listed in b_record (the lists that
+ * ue5m3_place_row_windows wrote; everything,
  * when a list overflowed) with the result of the issue-RZ kernel of ue5m3_gemm_issue_rz_bf16
  * on the exact encoded operands, which its producer warps decode from the codes and the raw
  * UE5M3 scale atoms (sf_raw of the quantizers) straight into shared memory.  The records are

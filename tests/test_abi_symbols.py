@@ -42,7 +42,7 @@ def test_version_and_status_strings():
     assert 4096 <= lib.ue5m3_amax_scratch_bytes() <= 65536
     lib.ue5m3_window_record_ints.restype = ctypes.c_size_t
     lib.ue5m3_window_record_ints.argtypes = [ctypes.c_int64]
-    assert lib.ue5m3_window_record_ints(300) == 4 + 4096 + 300
+    assert lib.ue5m3_window_record_ints(300) == 4 + 4096 + 2 * 300
 
 
 def test_argument_validation_needs_no_device():

@@ -70,10 +70,9 @@ def test_scale_window_record(b200):
         _, _, record = b200.pack_scales(scales, rows=128, k=64, block_size=16, two_dimensional=False, shift=0,
                                         want_raw=True)
         rec = record.tolist()
+        flags = rec[4 + b200.FALLBACK_MAX_ROWS:4 + b200.FALLBACK_MAX_ROWS + 128]
         if outside:
             assert rec[0] == 2 and rec[1] == 3, hex(code)
-            assert sorted(rec[4:6]) == [5, 77]
-            flags = rec[4 + b200.FALLBACK_MAX_ROWS:]
             assert [i for i, f in enumerate(flags) if f] == [5, 77]
         else:
             assert rec[0] == 0 and rec[1] == 0 and not any(rec[4:]), hex(code)
@@ -245,13 +244,24 @@ def test_one_pass_operand_quantizers_fill_the_window_record(b200):
     op = b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
                                    scale_target=448.0)
     assert op.window_counts() == (192, 192 * 7 - 1)
-    assert sorted(op.record[4:4 + 192].tolist()) == list(range(192))
+    assert op.flagged_rows() == list(range(192))
     # the transposed operand [128, 192]: blocks along the 192 rows of x; only columns 32..47 stay inside
     op_t = b200.quantize_fp4_operand(x, block_size=16, blocking=b200.BLOCK_COL, transposed=True, tensor_amax=amax,
                                      scale_target=448.0)
     listed, units = op_t.window_counts()
     assert listed == 112 and units == 112 * 12 - 1
-    assert sorted(op_t.record[4:4 + 112].tolist()) == [c for c in range(128) if not 32 <= c < 48]
+    assert op_t.flagged_rows() == [c for c in range(128) if not 32 <= c < 48]
+    # placement: column 3 holds the tensor maximum next to ones (its scales span the window: listed);
+    # every other flagged column is small as a whole and gets a window of its own
+    b200.place_row_windows(op_t, None)
+    listed_rows, placed = op_t.placement()
+    assert listed_rows == [3] and sorted(placed) == [c for c in range(128) if not 32 <= c < 48 and c != 3]
+    assert len(set(placed.values())) == 1 and next(iter(placed.values())) < -8
+    # the row-blocked operand: every row holds both the 1.0e3 band and blocks of ones -> in range of one
+    # window of its own, except row 5 with the 3.0e4 element
+    b200.place_row_windows(op, None)
+    listed_rows, placed = op.placement()
+    assert listed_rows == [5] and sorted(placed) == [r for r in range(192) if r != 5]
 
 
 def _bf16_path_product(b200, a, bt, *, block, two_d, amax_a, amax_b, monkeypatch):
@@ -299,14 +309,15 @@ def test_rows_and_columns_outside_the_scale_window_are_recomputed(b200, monkeypa
                                      tensor_amax=amax_a, scale_target=448.0)
     op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=block, blocking=b200.BLOCK_2D if two_d else b200.BLOCK_ROW,
                                      transposed=False, tensor_amax=amax_b, scale_target=448.0)
-    assert sorted(op_a.record[4:4 + len(rows_a)].tolist()) == rows_a and op_a.window_counts()[0] == len(rows_a)
-    assert sorted(op_b.record[4:4 + len(rows_b)].tolist()) == rows_b and op_b.window_counts()[0] == len(rows_b)
+    assert op_a.flagged_rows() == rows_a and op_b.flagged_rows() == sorted(rows_b)
     alpha = b200.encoded_global_alpha(amax_a, amax_b, 448.0, 448.0)
     bias = torch.randn(n, generator=g).cuda()
-    # the FP4 kernel alone gets the listed rows and columns wrong ...
+    # the FP4 kernel alone gets the flagged rows and columns wrong ...
     alone = b200.gemm_fp4(op_a.codes, op_a.scale_factors, op_b.codes, op_b.scale_factors, m=m, n=n, k=k,
                           shift_sum=op_a.shift + op_b.shift, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
     got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
+    # these rows mix blocks 2^-20 apart: no window of their own fits, all of them are listed
+    assert op_a.placement() == (rows_a, {}) and op_b.placement() == (sorted(rows_b), {})
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
     expect = (_bf16_path_product(b200, a, bt, block=block, two_d=two_d, amax_a=amax_a, amax_b=amax_b,
@@ -338,6 +349,7 @@ def test_an_overflowing_window_record_recomputes_the_whole_product(b200, monkeyp
     assert op_a.window_counts() == (m, m)
     alpha = b200.encoded_global_alpha(amax_a, amax_b, 448.0, 448.0)
     got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha)
+    assert op_a.record[2].item() == m  # every row's own scales span the window: all listed, more than fit
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
     expect = _bf16_path_product(b200, a, bt, block=16, two_d=False, amax_a=amax_a, amax_b=amax_b, monkeypatch=monkeypatch)
@@ -365,6 +377,7 @@ def test_alpha_formed_in_the_epilogue_equals_the_aten_expression(b200):
                                          scale_target=tb)
         assert op_a.window_counts()[0] == 1
         one = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=explicit, out_dtype=torch.bfloat16)
+        assert op_a.placement()[0] == [3]
         two = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=fused, out_dtype=torch.bfloat16)
         assert torch.equal(one, two)
         enc_a = b200.quantize_packed(a, block_size=16, tensor_amax=amax_a, scale_target=ta, packed=False,
@@ -378,9 +391,50 @@ def test_alpha_formed_in_the_epilogue_equals_the_aten_expression(b200):
     b200.check_gemm_status(dev)
 
 
+def test_small_rows_get_a_scale_window_of_their_own(b200, monkeypatch):
+    """Rows (tokens) of A and rows (output columns) of B that are small as a WHOLE - every block
+    2^-18 .. 2^-22 below the tensor's largest - leave the tensor's window but fit one placed at
+    their own largest scale: nothing is listed, the FP4 kernel computes them, the epilogue undoes
+    the per-row powers of two, and the result equals the BF16-issue product bit for bit."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(31)
+    m, k, n = 384, 512, 640
+    a = torch.randn(m, k, generator=g)
+    bt = torch.randn(n, k, generator=g)
+    small_a = [1, 64, 200, 383]
+    small_b = [0, 127, 128, 300, 639]
+    for i, r in enumerate(small_a):
+        a[r] *= 2.0 ** -(18 + i)
+    for i, r in enumerate(small_b):
+        bt[r] *= 2.0 ** -(19 + (i % 3))
+    a[7, 0:16] = 0.0   # an all-zero block in a placed-free row and ...
+    a[64, 32:48] = 0.0  # ... in a small row: its scale must not anchor the row's window
+    a, bt = a.to(torch.bfloat16), bt.to(torch.bfloat16)
+    amax_a = torch.tensor([float(a.float().abs().max())], device=dev)
+    amax_b = torch.tensor([float(bt.float().abs().max())], device=dev)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        op_a = b200.quantize_fp4_operand(a.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                         tensor_amax=amax_a, scale_target=448.0, shift_headroom=1)
+        op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                         tensor_amax=amax_b, scale_target=448.0)
+        assert op_a.flagged_rows() == small_a and op_b.flagged_rows() == small_b
+        alpha = b200.EpilogueAlpha.of(amax_a, amax_b, 448.0, 448.0)
+        bias = torch.randn(n, generator=g).cuda()
+        got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, bias=bias, out_dtype=out_dtype)
+        torch.cuda.synchronize()
+        b200.check_gemm_status(dev)
+        listed_a, placed_a = op_a.placement()
+        listed_b, placed_b = op_b.placement()
+        assert listed_a == [] and listed_b == [] and sorted(placed_a) == small_a and sorted(placed_b) == small_b
+        assert all(-24 <= shift <= -16 for shift in list(placed_a.values()) + list(placed_b.values()))
+        expect = (_bf16_path_product(b200, a, bt, block=16, two_d=False, amax_a=amax_a, amax_b=amax_b,
+                                     monkeypatch=monkeypatch) + bias).to(out_dtype)
+        assert torch.equal(got, expect)
+
+
 def _listed(op) -> list[int]:
-    count = min(op.window_counts()[0], 4096)
-    return sorted(op.record[4:4 + count].tolist())
+    return op.placement()[0]
 
 
 def test_squared_relu_down_proj_at_block_16_forward(b200):
@@ -404,12 +458,14 @@ def test_squared_relu_down_proj_at_block_16_forward(b200):
     y = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
-    listed = _listed(op_a)
-    print("squared-ReLU forward: rows listed", len(listed), "units outside", op_a.window_counts()[1])
-    assert 0 < len(listed) <= 4096 and op_b.window_counts() == (0, 0)
-    qx_all = oracle_quantize(x[listed].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
-    assert (qx_all["scale_codes"] < (10 << 3)).any(axis=1).all()  # every listed row does leave the window
-    rows = torch.tensor(sorted(set(listed[:24] + [0, 127, 128, 4096, 8191])))
+    listed, placed = op_a.placement()
+    flagged = op_a.flagged_rows()
+    print("squared-ReLU forward: rows flagged", len(flagged), "placed", len(placed), "listed", len(listed),
+          "units outside", op_a.window_counts()[1])
+    assert 0 < len(flagged) <= 4096 and op_b.window_counts() == (0, 0) and sorted(listed + list(placed)) == flagged
+    qx_all = oracle_quantize(x[flagged].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
+    assert (qx_all["scale_codes"] < (10 << 3)).any(axis=1).all()  # every flagged row does leave the tensor's window
+    rows = torch.tensor(sorted(set(listed[:16] + sorted(placed)[:16] + [0, 127, 128, 4096, 8191])))
     col_bands = [0, 256, 2048, 4080]
     cols = torch.cat([torch.arange(c, c + 16) for c in col_bands])
     qx = oracle_quantize(x[rows].float(), block=16, blocking=o.BLOCK_ROW, amax=float(ax.item()))
@@ -442,10 +498,12 @@ def test_squared_relu_down_proj_at_block_16_weight_gradient_operand(b200):
     dw = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
-    listed = _listed(op_b)
-    print("squared-ReLU weight gradient: columns listed", len(listed), "units outside", op_b.window_counts()[1])
-    assert 0 < len(listed) <= 4096 and op_a.window_counts() == (0, 0)
-    cols = torch.tensor(sorted(set(listed[:24] + [0, 255, 256, 21503])))
+    listed, placed = op_b.placement()
+    flagged = op_b.flagged_rows()
+    print("squared-ReLU weight gradient: columns flagged", len(flagged), "placed", len(placed), "listed", len(listed),
+          "units outside", op_b.window_counts()[1])
+    assert 0 < len(flagged) <= 4096 and op_a.window_counts() == (0, 0) and sorted(listed + list(placed)) == flagged
+    cols = torch.tensor(sorted(set(listed[:16] + sorted(placed)[:16] + [0, 255, 256, 21503])))
     rows = torch.tensor([0, 1, 127, 128, 511, 1023])
     q_dy = oracle_quantize(dy[:, rows].float(), block=16, blocking=o.BLOCK_COL, amax=float(ady.item()))
     q_x = oracle_quantize(x[:, cols].float(), block=16, blocking=o.BLOCK_COL, amax=float(ax.item()))

@@ -62,7 +62,7 @@ struct Plan {
 
 __device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, int M, int N) {
     Plan plan;
-    const int na = __ldg(rec_a), nb = __ldg(rec_b);
+    const int na = __ldg(rec_a + kRecListed), nb = __ldg(rec_b + kRecListed);
     plan.full = na > kRecMaxRows || nb > kRecMaxRows;
     plan.na = plan.full ? 0 : na;
     plan.nb = plan.full ? 0 : nb;

@@ -69,7 +69,21 @@ struct Fp4Params {
     const uint8_t* sfa;  // [ceil(M/128)][K/64][512]
     const uint8_t* sfb;  // [ceil(N/128)][K/64][512]
     int tiles_m, tiles_n;
+    // window records of the operands (null: none).  Rows that got a scale window of their own
+    // (window_place.cu) carry an extra exponent there; the epilogue multiplies by 2^(a[row] + b[col]).
+    const int* rec_a;
+    const int* rec_b;
+    const int* row_shift_a;  // set inside the kernel: null unless the record says that rows were placed
+    const int* row_shift_b;
 };
+
+// the kernel's parameters with the per-row exponent tables resolved from the records
+__device__ __forceinline__ Fp4Params resolve_row_shifts(const Fp4Params& p) {
+    Fp4Params q = p;
+    q.row_shift_a = (p.rec_a && __ldg(p.rec_a + kRecPlaced) > 0) ? rec_row_shift(p.rec_a, p.M) : nullptr;
+    q.row_shift_b = (p.rec_b && __ldg(p.rec_b + kRecPlaced) > 0) ? rec_row_shift(p.rec_b, p.N) : nullptr;
+    return q;
+}
 
 struct __align__(8) Fp4Barriers {
     unsigned long long full[kFStages];
@@ -111,6 +125,7 @@ __host__ __device__ constexpr uint32_t make_idesc_fp4(int m, int n) {
 // (columns [tile_n * 256 + h * 128, + 128)): rescale by 2^shift, snap, alpha, bias, cast.
 __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t (&v)[4][32], long long row,
                                               int tile_n, int h, float alpha) {
+    const float row_factor = p.row_shift_a ? __fmul_rn(p.rescale, exp2_int(__ldg(p.row_shift_a + row))) : p.rescale;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
@@ -118,7 +133,8 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
         float c[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            float x = __fmul_rn(__uint_as_float(v[chunk][i]), p.rescale);
+            float x = __fmul_rn(__uint_as_float(v[chunk][i]), row_factor);
+            if (p.row_shift_b && col0 + i < p.N) x = __fmul_rn(x, exp2_int(__ldg(p.row_shift_b + col0 + i)));
             if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
             if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
             c[i] = x;
@@ -182,6 +198,8 @@ constexpr uint32_t kStageBytesPerWarp = 32 * 128;
 __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const uint32_t (&v)[4][32],
                                                            long long row0, int tile_n, int h, float alpha,
                                                            unsigned char* stage, int lane) {
+    float row_factor = p.rescale;
+    if (p.row_shift_a && row0 + lane < p.M) row_factor = __fmul_rn(row_factor, exp2_int(__ldg(p.row_shift_a + row0 + lane)));
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + pass * 64;
@@ -191,7 +209,8 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, c
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int idx = pass * 64 + c * 8 + e;
-                float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), p.rescale);
+                float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), row_factor);
+                if (p.row_shift_b) x = __fmul_rn(x, exp2_int(__ldg(p.row_shift_b + col0 + c * 8 + e)));
                 if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
                 if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
                 if (p.bias) {
@@ -409,6 +428,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;          // TMEM lane quadrant
         const int h = (warp - 2) >> 2;   // column half of the tile
         const float alpha = alpha_value(p.alpha);
+        const Fp4Params pq = resolve_row_shifts(p);
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             int tile_m, tile_n;
@@ -428,7 +448,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
             const long long row = (long long)tile_m * kFM + q * 32 + lane;
             if (row >= p.M) continue;
-            fp4_store_row(p, v, row, tile_n, h, alpha);
+            fp4_store_row(pq, v, row, tile_n, h, alpha);
         }
     }
 
@@ -705,6 +725,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int q = warp & 3;
         const int h = (warp - 2) >> 2;
         const float alpha = alpha_value(p.alpha);
+        const Fp4Params pq = resolve_row_shifts(p);
         const uint32_t tmem_empty_leader = map_to_cta(smem_u32(&bars->tmem_empty), 0);
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
@@ -727,13 +748,13 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const bool staged = p.out_dtype == UE5M3_DTYPE_BF16 && (p.ldo % 8) == 0 &&
                                 ((uintptr_t)p.out % 16) == 0 && tile_n * kFN + (h + 1) * (kFN / 2) <= p.N;
             if (staged) {
-                fp4_store_rows_staged_bf16(p, v, row0, tile_n, h, alpha,
+                fp4_store_rows_staged_bf16(pq, v, row0, tile_n, h, alpha,
                                            stage_base + (warp - 2) * kStageBytesPerWarp, lane);
                 continue;
             }
             const long long row = row0 + lane;
             if (row >= p.M) continue;
-            fp4_store_row(p, v, row, tile_n, h, alpha);
+            fp4_store_row(pq, v, row, tile_n, h, alpha);
         }
     }
 
@@ -865,7 +886,7 @@ using namespace ue5m3;
 
 extern "C" size_t ue5m3_window_record_ints(int64_t operand_rows) {
     if (operand_rows <= 0) return 0;
-    return (size_t)kRecHeader + (size_t)kRecMaxRows + (size_t)operand_rows;
+    return (size_t)kRecHeader + (size_t)kRecMaxRows + 2 * (size_t)operand_rows;
 }
 
 extern "C" size_t ue5m3_packed_scales_bytes(int64_t rows, int64_t K) {
@@ -895,7 +916,8 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
                               const uint8_t* b_sf, int64_t M, int64_t N, int64_t K, int shift_sum,
                               int snap, const float* alpha_dev, const float* amax_a_dev,
                               const float* amax_b_dev, float inv_denominator, const void* bias,
-                              int bias_dtype, void* out, int out_dtype, int64_t ldo, int* status_dev,
+                              int bias_dtype, void* out, int out_dtype, int64_t ldo,
+                              const int* a_record, const int* b_record, int* status_dev,
                               void* stream_v) {
     if (!a_codes || !a_sf || !b_codes || !b_sf || !out || M <= 0 || N <= 0 || K <= 0)
         return UE5M3_ERR_INVALID_ARGUMENT;
@@ -926,6 +948,7 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
     p.sfa = a_sf; p.sfb = b_sf;
+    p.rec_a = a_record; p.rec_b = b_record; p.row_shift_a = nullptr; p.row_shift_b = nullptr;
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
     const int64_t tiles = tiles_m * tiles_n;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);

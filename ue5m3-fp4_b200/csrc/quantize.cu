@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
 #pragma unroll
             for (int h = 0; h < B / 16; ++h) {
                 s.sf_t[c][g * (B / 16) + h] = (uint8_t)code4;
-                s.sf_raw_t[c][g * (B / 16) + h] = (uint8_t)code;
+                s.sf_raw_t[c][g * (B / 16) + h] = m == 0.0f ? (uint8_t)0 : (uint8_t)code;   // 0 marks an all-zero block
             }
         }
         uint32_t nib[B];
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
             if (ka < k_atoms) {
                 uint32_t word = *reinterpret_cast<const uint32_t*>(&s.sf_t[c][4 * half]);
                 uint32_t raw_word = *reinterpret_cast<const uint32_t*>(&s.sf_raw_t[c][4 * half]);
-                if (orow >= a.cols) { word = 0x38383838u; raw_word = 0x78787878u; }
+                if (orow >= a.cols) { word = 0x38383838u; raw_word = 0u; }
                 const int64_t at = ((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3);
                 a.sf_t[at] = word;
                 if (a.sf_raw_t) a.sf_raw_t[at] = raw_word;
@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(TileArgs a) {
                     const int64_t prow = orow + kTileCols;
                     const int64_t pat = ((prow >> 7) * k_atoms + ka) * 128 + (prow & 31) * 4 + ((prow >> 5) & 3);
                     a.sf_t[pat] = 0x38383838u;
-                    if (a.sf_raw_t) a.sf_raw_t[pat] = 0x78787878u;
+                    if (a.sf_raw_t) a.sf_raw_t[pat] = 0u;
                 }
             }
         }

@@ -112,7 +112,7 @@ quantize_operand_kernel(const OperandArgs a) {
             }
             bool outside;
             sf_bytes |= ue4m3_window_byte(code[u], rebias, outside) << (8 * u);
-            raw_bytes |= code[u] << (8 * u);
+            raw_bytes |= (m[u] == 0.0f ? 0u : code[u]) << (8 * u);   // 0 marks an all-zero block
             if (outside && valid && a.sf) {
                 ++bad_units;
                 window_record_row(a.window_record, row);
@@ -185,12 +185,12 @@ quantize_operand_kernel(const OperandArgs a) {
             uint32_t* raw_word = a.sf_raw ? a.sf_raw + (word - a.sf) : nullptr;
             if (U == 4) {
                 *word = valid ? sf_bytes : 0x38383838u;
-                if (raw_word) *raw_word = valid ? raw_bytes : 0x78787878u;
+                if (raw_word) *raw_word = valid ? raw_bytes : 0u;
             } else {
                 const int half_index = (int)((col0 % 64) / 32);
                 reinterpret_cast<uint16_t*>(word)[half_index] = valid ? (uint16_t)sf_bytes : (uint16_t)0x3838u;
                 if (raw_word)
-                    reinterpret_cast<uint16_t*>(raw_word)[half_index] = valid ? (uint16_t)raw_bytes : (uint16_t)0x7878u;
+                    reinterpret_cast<uint16_t*>(raw_word)[half_index] = valid ? (uint16_t)raw_bytes : (uint16_t)0u;
             }
         }
     }
@@ -442,7 +442,7 @@ quantize_operand_t_kernel(const OperandTArgs a) {
             block_scale_converged(m[h][j], ts, code, scale);
             bool outside;
             sf_pair[j] |= ue4m3_window_byte(code, rebias, outside) << (8 * h);
-            raw_pair[j] |= code << (8 * h);
+            raw_pair[j] |= (m[h][j] == 0.0f ? 0u : code) << (8 * h);   // 0 marks an all-zero block
             if (outside && rows_valid && col + j < a.cols) {
                 ++bad_units;
                 window_record_row(a.window_record, col + j);
@@ -487,7 +487,7 @@ quantize_operand_t_kernel(const OperandTArgs a) {
             const int64_t byte_offset = (((orow >> 7) * k_atoms + ka) * 128 + (orow & 31) * 4 + ((orow >> 5) & 3)) * 4 + kb0;
             *reinterpret_cast<uint16_t*>(a.sf_t + byte_offset) = orow < a.cols ? (uint16_t)sf_pair[j] : (uint16_t)0x3838u;
             if (a.sf_raw_t)
-                *reinterpret_cast<uint16_t*>(a.sf_raw_t + byte_offset) = orow < a.cols ? (uint16_t)raw_pair[j] : (uint16_t)0x7878u;
+                *reinterpret_cast<uint16_t*>(a.sf_raw_t + byte_offset) = orow < a.cols ? (uint16_t)raw_pair[j] : (uint16_t)0u;
         }
     }
     window_record_units(a.window_record, bad_units);

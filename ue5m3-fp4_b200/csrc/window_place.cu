@@ -1,0 +1,124 @@
+// Row-wise placement of the UE4M3 scale window.
+//
+// The operand quantizers re-bias every UE5M3 block scale of a tensor by ONE power of two so
+// that the tensor's largest possible scale sits at the top of UE4M3's 15 binades; a block whose
+// scale falls below them gets its row flagged.  Most such rows are simply small as a whole
+// (a token with a small gradient, a feature that hardly fires): their own largest scale is far
+// below the tensor's, and their blocks fit 15 binades once the window is placed at the ROW's
+// largest scale.  Scaling one operand row by a power of two scales every product of the output
+// row (A operand) or column (B operand) it feeds by the same power of two, which the
+// round-toward-zero accumulation commutes with exactly, so the GEMM epilogue undoes it with
+// one exact multiply.
+//
+// This kernel visits the flagged rows of both operands of a product, reads their raw UE5M3
+// scale bytes, and for each row either rewrites its UE4M3 bytes with the row's own shift
+// (stored as the difference to the tensor's shift in the record) or, when the row's scales
+// span more than the window, lists it for the recomputation pass.  With no flagged row every
+// CTA returns after reading two integers.  No reference counterpart (the reference has no
+// hardware scale type).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "abi_common.cuh"
+#include "window_record.cuh"
+
+namespace ue5m3 {
+
+struct PlaceOperand {
+    uint8_t* sf;          // UE4M3 atoms, rewritten for placed rows
+    const uint8_t* raw;   // raw UE5M3 atoms (0 = all-zero block)
+    int* rec;
+    int rows;
+    int shift;            // the tensor's shift
+};
+
+struct PlaceArgs {
+    PlaceOperand op[2];
+    int k_atoms;          // K / 64
+};
+
+__device__ __forceinline__ void place_rows(const PlaceOperand& o, int k_atoms, int warp_global, int warps_total,
+                                           int lane) {
+    if (!o.rec || __ldg(o.rec + kRecFlagged) == 0) return;
+    const int* flags = rec_flags(o.rec);
+    int* row_shift = rec_row_shift(o.rec, o.rows);
+    for (int row = warp_global; row < o.rows; row += warps_total) {
+        if (flags[row] == 0) continue;
+        const int64_t base = ((int64_t)(row >> 7) * k_atoms) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+        // largest and smallest scale byte of the row's non-zero blocks
+        uint32_t top = 0u, bottom = 0xFFu;
+        for (int ka = lane; ka < k_atoms; ka += 32) {
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(o.raw + base + (int64_t)ka * 512);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t byte = (word >> (8 * b)) & 0xFFu;
+                if (byte != 0u) {
+                    top = max(top, byte);
+                    bottom = min(bottom, byte);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            top = max(top, __shfl_xor_sync(0xFFFFFFFFu, top, d));
+            bottom = min(bottom, __shfl_xor_sync(0xFFFFFFFFu, bottom, d));
+        }
+        if (top == 0u) continue;  // nothing but zero blocks
+        // smallest shift that brings the largest byte to 0x7E or below: byte - ((8 + s) << 3) <= 0x7E
+        int shift = ((int)top - 0x7E + 7) >> 3;   // ceil((top - 0x7E) / 8), also for negative values
+        shift -= 8;
+        const int rebias = (8 + shift) << 3;
+        if ((int)bottom - rebias < 8) {
+            // the row's own scales span more than the window: recompute it
+            if (lane == 0) {
+                const int slot = atomicAdd(o.rec + kRecListed, 1);
+                if (slot < kRecMaxRows) rec_list(o.rec)[slot] = row;
+            }
+            continue;
+        }
+        for (int ka = lane; ka < k_atoms; ka += 32) {
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(o.raw + base + (int64_t)ka * 512);
+            uint32_t out = 0u;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t byte = (word >> (8 * b)) & 0xFFu;
+                out |= (byte == 0u ? 0x38u : (uint32_t)((int)byte - rebias)) << (8 * b);
+            }
+            *reinterpret_cast<uint32_t*>(o.sf + base + (int64_t)ka * 512) = out;
+        }
+        if (lane == 0) {
+            row_shift[row] = shift - o.shift;
+            atomicAdd(o.rec + kRecPlaced, 1);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) place_row_windows_kernel(const PlaceArgs args) {
+    const int lane = threadIdx.x & 31;
+    const int warp_global = (int)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int warps_total = (int)gridDim.x * 8;
+    place_rows(args.op[0], args.k_atoms, warp_global, warps_total, lane);
+    place_rows(args.op[1], args.k_atoms, warp_global, warps_total, lane);
+}
+
+}  // namespace ue5m3
+
+using namespace ue5m3;
+
+extern "C" int ue5m3_place_row_windows(uint8_t* a_sf, const uint8_t* a_sf_raw, int* a_record, int64_t a_rows,
+                                       int a_shift, uint8_t* b_sf, const uint8_t* b_sf_raw, int* b_record,
+                                       int64_t b_rows, int b_shift, int64_t K, void* stream_v) {
+    if (K <= 0 || K % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if ((a_record && (!a_sf || !a_sf_raw || a_rows <= 0)) || (b_record && (!b_sf || !b_sf_raw || b_rows <= 0)))
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!a_record && !b_record) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (a_rows > 0x7FFFFFFF || b_rows > 0x7FFFFFFF || K / 64 > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    if (((uintptr_t)a_sf % 4) || ((uintptr_t)a_sf_raw % 4) || ((uintptr_t)b_sf % 4) || ((uintptr_t)b_sf_raw % 4))
+        return UE5M3_ERR_ALIGNMENT;
+    PlaceArgs args;
+    args.op[0] = PlaceOperand{a_sf, a_sf_raw, a_record, (int)a_rows, a_shift};
+    args.op[1] = PlaceOperand{b_sf, b_sf_raw, b_record, (int)b_rows, b_shift};
+    args.k_atoms = (int)(K / 64);
+    place_row_windows_kernel<<<sm_count(), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(args);
+    return check_launch();
+}

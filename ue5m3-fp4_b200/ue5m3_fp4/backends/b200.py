@@ -448,9 +448,10 @@ def pack_scales(scales: Tensor, *, rows: int, k: int, block_size: int, two_dimen
 def gemm_fp4(
     a_codes: Tensor, a_sf: Tensor, b_codes: Tensor, b_sf: Tensor, *, m: int, n: int, k: int, shift_sum: int,
     snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None, bias: Tensor | None = None,
-    out_dtype: torch.dtype = torch.float32,
+    out_dtype: torch.dtype = torch.float32, a_record: Tensor | None = None, b_record: Tensor | None = None,
 ) -> Tensor:
-    """out[M,N] on packed E2M1 codes + packed scales with the FP4 block-scaled tensor cores."""
+    """out[M,N] on packed E2M1 codes + packed scales with the FP4 block-scaled tensor cores;
+    ``a_record`` / ``b_record``: window records whose placed rows carry a shift of their own."""
 
     _require_cuda(a_codes, "a_codes")
     if k % 64:
@@ -463,8 +464,8 @@ def gemm_fp4(
             a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(), m, n, k, shift_sum,
             int(bool(snap)), *_alpha_arguments(alpha, a_codes.device), _native.ptr(bias),
             _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
-            _native.dtype_code(out_dtype), n, gemm_status(a_codes.device).data_ptr(),
-            _native.stream_ptr(a_codes.device),
+            _native.dtype_code(out_dtype), n, _native.ptr(a_record), _native.ptr(b_record),
+            gemm_status(a_codes.device).data_ptr(), _native.stream_ptr(a_codes.device),
         )
     _native.check(status, "ue5m3_gemm_fp4")
     return out
@@ -495,14 +496,36 @@ class Fp4Operand:
     k: int
     raw_scale_factors: Tensor | None = None
     record: Tensor | None = None
+    placed: bool = False   # place_row_windows has run on this operand
 
     def window_counts(self) -> tuple[int, int]:
-        """(rows listed for recomputation, 16-element units outside the window); synchronises."""
+        """(rows the quantizer flagged, 16-element units outside the window at the tensor's
+        shift); synchronises."""
 
         if self.record is None:
             return (0, 0)
-        listed, units = self.record[:2].tolist()
-        return int(listed), int(units)
+        flagged, units = self.record[:2].tolist()
+        return int(flagged), int(units)
+
+    def flagged_rows(self) -> list[int]:
+        """Rows with a block scale outside the window at the tensor's shift; synchronises."""
+
+        if self.record is None:
+            return []
+        flags = self.record[4 + FALLBACK_MAX_ROWS:4 + FALLBACK_MAX_ROWS + self.rows]
+        return torch.nonzero(flags).flatten().tolist()
+
+    def placement(self) -> tuple[list[int], dict[int, int]]:
+        """After ``place_row_windows``: (rows listed for recomputation, {row: its shift minus the
+        tensor's} for rows that got a window of their own); synchronises."""
+
+        if self.record is None:
+            return [], {}
+        head = self.record[:4].tolist()
+        listed = sorted(self.record[4:4 + min(head[2], FALLBACK_MAX_ROWS)].tolist())
+        shifts = self.record[4 + FALLBACK_MAX_ROWS + self.rows:4 + FALLBACK_MAX_ROWS + 2 * self.rows]
+        placed = {int(r): int(shifts[r]) for r in self.flagged_rows() if r not in set(listed)} if head[3] else {}
+        return listed, placed
 
 
 def quantize_fp4_operand(
@@ -636,6 +659,37 @@ def hadamard_amax_transposed(x: Tensor) -> Tensor:
     return out
 
 
+def place_row_windows(a: Fp4Operand | None, b: Fp4Operand | None) -> None:
+    """Give the flagged rows of the two operands of one product scale windows of their own where
+    their scales fit one, and list the rest for the recomputation pass (ue5m3_place_row_windows;
+    one launch, returns at once on the device when nothing is flagged).  Idempotence is not
+    needed: ``gemm_fp4_operands`` calls it once per operand pair; an operand that is reused
+    (a cached weight) is placed once, the flag of that is kept on the operand."""
+
+    todo = [op for op in (a, b) if op is not None and not op.placed]
+    if not todo:
+        return
+    first = todo[0]
+    second = todo[1] if len(todo) > 1 else None
+    if second is not None and second.k != first.k:
+        raise ValueError("operands of one product share the reduction length")
+    for op in todo:
+        if op.record is None or op.raw_scale_factors is None:
+            raise ValueError("packed operands must carry their raw scales and window records")
+    with torch.cuda.device(first.codes.device):
+        status = _native.load().ue5m3_place_row_windows(
+            first.scale_factors.data_ptr(), first.raw_scale_factors.data_ptr(), first.record.data_ptr(), first.rows,
+            first.shift,
+            _native.ptr(None if second is None else second.scale_factors),
+            _native.ptr(None if second is None else second.raw_scale_factors),
+            _native.ptr(None if second is None else second.record), 0 if second is None else second.rows,
+            0 if second is None else second.shift, first.k, _native.stream_ptr(first.codes.device),
+        )
+    _native.check(status, "ue5m3_place_row_windows")
+    for op in todo:
+        op.placed = True
+
+
 _window_log: list | None = None
 
 
@@ -654,11 +708,13 @@ def window_log_summary() -> dict:
     entries = _window_log or []
     if not entries:
         return {"products": 0}
-    heads = torch.stack([torch.stack((a[:2], b[:2])) for a, b, _ in entries]).tolist()
+    heads = torch.stack([torch.stack((a[2:4], b[2:4])) for a, b, _ in entries]).tolist()
     summary = {"products": len(entries), "with_listed_rows": 0, "with_listed_columns": 0, "recomputed_in_full": 0,
                "listed_rows_total": 0, "listed_columns_total": 0, "recomputed_tflop": 0.0, "total_tflop": 0.0,
-               "in_full_by_shape": {}, "listed_by_shape": {}}
-    for ((rows_a, _), (rows_b, _)), (_, _, (m, n, k)) in zip(heads, entries):
+               "in_full_by_shape": {}, "listed_by_shape": {}, "rows_placed_total": 0, "columns_placed_total": 0}
+    for ((rows_a, placed_a), (rows_b, placed_b)), (_, _, (m, n, k)) in zip(heads, entries):
+        summary["rows_placed_total"] += placed_a
+        summary["columns_placed_total"] += placed_b
         flop = 2.0 * m * n * k / 1e12
         summary["total_tflop"] += flop
         shape = f"{m}x{n}x{k}"
@@ -689,10 +745,12 @@ def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tenso
 
     if a.k != b.k:
         raise ValueError("a and b have incompatible K dimensions")
-    out = gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
-                   shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype)
     if a.record is None or b.record is None or a.raw_scale_factors is None or b.raw_scale_factors is None:
         raise ValueError("packed operands must carry their raw scales and window records")
+    place_row_windows(a, b)
+    out = gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
+                   shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype,
+                   a_record=a.record, b_record=b.record)
     with torch.cuda.device(out.device):
         status = _native.load().ue5m3_gemm_fp4_fallback(
             a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(),
@@ -967,6 +1025,7 @@ __all__ = [
     "pack_scales",
     "quantize_fp4_operand",
     "new_window_record",
+    "place_row_windows",
     "log_window_records",
     "window_log_summary",
     "poll_gemm_status",
