@@ -204,6 +204,64 @@ def test_inference_lifecycle_training_replay():
     assert outputs[2].shape == (32, 64) and torch.isfinite(outputs[2].float()).all()
 
 
+def test_packed_weight_file_feeds_the_frozen_inference_path(tmp_path, monkeypatch):
+    """export_packed_weight / load_packed_weight: the weight of a frozen layer goes to a packed
+    file (0.5625 byte per element) and comes back as the forward operand; outputs are identical
+    and the weight is not quantized again."""
+
+    from ue5m3_fp4.backends import b200
+    from ue5m3_fp4.packed import PackedFP4Tensor
+    from ue5m3_fp4.scaling import FP4InferenceScalingController
+
+    monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+
+    def frozen_model(seed):
+        model = torch.nn.Sequential()
+        model.add_module("proj", _layer(256, 192, bias=True, name="proj", seed=seed))
+        model.eval()
+        controller = FP4InferenceScalingController(model, activation_mode="current_tensor",
+                                                   checkpoint_identity={"name": "synthetic"})
+        controller.reset_after_checkpoint_load()
+        controller.calibrate_and_freeze_weights()
+        controller.begin_measurement()
+        return model
+
+    first = frozen_model(seed=8)
+    x = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        expect = first(x)
+    path = tmp_path / "proj.ue5m3"
+    first.proj.export_packed_weight(path)
+    weight = first.proj.weight
+    assert path.stat().st_size < weight.numel() * 0.5625 + 1024
+    packed = PackedFP4Tensor.load(path, "cuda")
+    direct = b200.quantize_packed(weight.detach(), block_size=16, blocking=b200.BLOCK_2D,
+                                  tensor_amax=b200.tensor_amax(weight.detach()).reshape(1), packed=True, packed_t=False)
+    assert torch.equal(packed.codes, direct.codes) and torch.equal(packed.scales, direct.scales)
+    assert torch.equal(packed.dequantize(), b200.dequantize_packed(
+        direct.codes, direct.scales, rows=192, cols=256, block_size=16, two_dimensional=True,
+        tensor_amax=b200.tensor_amax(weight.detach()).reshape(1)))
+
+    second = frozen_model(seed=8)   # the same weights, loaded "from a checkpoint"
+    second.proj.load_packed_weight(path)
+    calls = []
+    original = b200.quantize_fp4_operand
+
+    def counting(tensor, **kwargs):
+        calls.append(tuple(tensor.shape))
+        return original(tensor, **kwargs)
+
+    monkeypatch.setattr(b200, "quantize_fp4_operand", counting)
+    with torch.no_grad():
+        got = second(x)
+        again = second(x)
+    assert torch.equal(got, expect) and torch.equal(again, expect)
+    assert calls == [(64, 256), (64, 256)]  # activations only: the weight came from the file
+    other = frozen_model(seed=9)
+    with pytest.raises(ValueError, match="another tensor amax"):
+        other.proj.load_packed_weight(path)
+
+
 def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monkeypatch):
     """On the FP4 path the forward saves the packed weight-gradient operand of X (codes +
     scale atoms, the raw scale bytes and the small window record) instead of the bf16

@@ -222,3 +222,38 @@ def test_linear_fails_closed_on_cpu_and_reports_contract_strings():
         layer(torch.ones(4, 63, dtype=torch.bfloat16))
     with pytest.raises(ValueError, match="unknown UE5M3 linear backend"):
         UE5M3Linear(4, 4, backend="fastest")
+
+
+def test_packed_tensor_file_round_trip_on_the_host(tmp_path):
+    """The storable packed form (codes + UE5M3 scale bytes + metadata): written and read back
+    bit for bit, with the tensor amax kept as its exact fp32 bit pattern; malformed files are
+    refused."""
+
+    from ue5m3_fp4.packed import PackedFP4Tensor
+
+    g = torch.Generator().manual_seed(0)
+    for rows, cols, block, blocking in ((5, 40, 16, "row"), (70, 96, 32, "2d")):
+        scale_rows = rows if blocking == "row" else (rows + block - 1) // block
+        packed = PackedFP4Tensor(
+            torch.randint(0, 256, (rows, (cols + 1) // 2), generator=g, dtype=torch.int32).to(torch.uint8),
+            torch.randint(1, 0xF8, (scale_rows, (cols + block - 1) // block), generator=g, dtype=torch.int32).to(torch.uint8),
+            rows, cols, block, blocking, tensor_amax=float(torch.tensor(0.1, dtype=torch.float32)), scale_target=448.0,
+            name="layers.3.mixer.down_proj")
+        path = tmp_path / f"{blocking}.ue5m3"
+        packed.save(path)
+        back = PackedFP4Tensor.load(path)
+        assert torch.equal(back.codes, packed.codes) and torch.equal(back.scales, packed.scales)
+        assert (back.rows, back.cols, back.block_size, back.blocking, back.name) == (rows, cols, block, blocking, packed.name)
+        assert back.tensor_amax == packed.tensor_amax and back.scale_target == 448.0
+        assert path.stat().st_size < 8 + 8 + 1024 + packed.codes.numel() + packed.scales.numel()
+    with pytest.raises(ValueError, match="codes must be"):
+        PackedFP4Tensor(torch.zeros(3, 3, dtype=torch.uint8), torch.zeros(3, 1, dtype=torch.uint8), 3, 16, 16, "row", 1.0, 448.0)
+    (tmp_path / "bad").write_bytes(b"not a packed tensor at all")
+    with pytest.raises(ValueError, match="not a packed"):
+        PackedFP4Tensor.load(tmp_path / "bad")
+    data = path.read_bytes()
+    (tmp_path / "short").write_bytes(data[:-10])
+    with pytest.raises(ValueError, match="truncated"):
+        PackedFP4Tensor.load(tmp_path / "short")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        back.gemm_operand()

@@ -513,6 +513,48 @@ class UE5M3Linear(torch.nn.Module):
                 self._inference["frozen_weights"].get("forward.w"), plan.path, plan.block,
                 self.recipe.two_dimensional_weights)
 
+    def export_packed_weight(self, path) -> None:
+        """Write this layer's weight, quantized with its FROZEN amax, as a packed FP4 tensor file
+        (``ue5m3_fp4.packed.PackedFP4Tensor``): what a quantized-evaluation run needs of the
+        weight, at 0.5625 byte per element.  Requires the post-load lifecycle to have frozen the
+        weight scale."""
+
+        from ue5m3_fp4.packed import PackedFP4Tensor
+
+        frozen = self._inference["frozen_weights"].get("forward.w") if self._inference["active"] else None
+        if frozen is None:
+            raise RuntimeError("Weight amax has not been frozen after checkpoint load")
+        PackedFP4Tensor.quantize(
+            self.weight.detach(), block_size=self.recipe.block_size, two_dimensional=self.recipe.two_dimensional_weights,
+            tensor_amax=float(frozen), scale_target=self.recipe.scale_target_for("weight", self.module_name),
+            name=self.module_name).save(path)
+
+    def load_packed_weight(self, path) -> None:
+        """Install a packed weight written by ``export_packed_weight`` as this layer's forward
+        operand, so that no forward pass quantizes the weight.  The file must describe this
+        layer's weight under this layer's recipe and frozen amax; the operand is dropped again
+        as soon as the parameter is written to."""
+
+        from ue5m3_fp4.packed import PackedFP4Tensor
+
+        plan = _OperandPlan(self)
+        if plan.path != "fp4":
+            raise RuntimeError("packed weights feed the FP4 tensor-core path (UE5M3_GEMM_PATH=fp4)")
+        frozen = self._inference["frozen_weights"].get("forward.w") if self._inference["active"] else None
+        if frozen is None:
+            raise RuntimeError("Weight amax has not been frozen after checkpoint load")
+        packed = PackedFP4Tensor.load(path, self.weight.device)
+        expect = (self.out_features, self.in_features, self.recipe.block_size,
+                  "2d" if self.recipe.two_dimensional_weights else "row",
+                  self.recipe.scale_target_for("weight", self.module_name))
+        found = (packed.rows, packed.cols, packed.block_size, packed.blocking, packed.scale_target)
+        if found != expect:
+            raise ValueError(f"packed weight {found} does not match this layer {expect}")
+        if packed.tensor_amax != float(torch.tensor(float(frozen), dtype=torch.float32)):
+            raise ValueError("packed weight was quantized with another tensor amax than the frozen one")
+        reference = self._reference_tensor(float(frozen), self.weight)
+        self._remember_packed_frozen_weight(self.weight, reference, plan, packed.gemm_operand(shift_headroom=1))
+
     def _packed_frozen_weight(self, weight: torch.Tensor, reference: torch.Tensor, plan):
         cached = self.__dict__.get("_packed_weight_cache")
         if cached is not None and cached[0] == self._packed_weight_key(weight, reference, plan):
