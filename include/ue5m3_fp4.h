@@ -210,6 +210,18 @@ int ue5m3_place_row_windows(uint8_t *a_sf, const uint8_t *a_sf_raw, int *a_recor
                             int64_t b_rows, int b_shift, int64_t K, void *stream);
 
 /*
+ * histogram_dev[b] += number of blocks of the operand whose UE5M3 scale byte is b (256
+ * unsigned 64-bit counters, accumulated: clear them to start afresh); bin 0 = blocks whose
+ * elements are all zero.  Reads the raw scale atoms (sf_raw) that the one-pass operand
+ * quantizers write, i.e. 1/16 byte per element; two_d != 0 counts a block x block tile once.
+ * Device-side counterpart of the block-scale diagnostics of
+ * reproduce/scale_target/capture_scale_target_histograms.py:257-366 (block count, zero blocks,
+ * saturated blocks = byte 0xF7, the scale-code distribution).
+ */
+int ue5m3_scale_byte_histogram(const uint8_t *sf_raw, int64_t rows, int64_t K, int block, int two_d,
+                               unsigned long long *histogram_dev, void *stream);
+
+/*
  * UE5M3 scale bytes -> the block-scaled tensor core's UE4M3 scale-factor layout.
  * scales: [rows, K/block] (two_d == 0) or [ceil(rows/block), K/block] (two_d != 0) as written
  * by ue5m3_quantize for a K-major operand.  sf_out: ue5m3_packed_scales_bytes(rows, K) bytes,

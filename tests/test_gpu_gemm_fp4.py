@@ -27,10 +27,10 @@ def b200():
 def _expected_scale_layout(scales: np.ndarray, rows: int, k: int, block: int, two_d: bool, shift: int,
                            raw: bool = False) -> np.ndarray:
     """The 512-byte atoms: UE4M3 bytes (re-biased, clamped to the normal range, 1.0 = 0x38 in the
-    padding rows) or, with ``raw``, the unmodified UE5M3 bytes (1.0 = 0x78 in the padding rows)."""
+    padding rows) or, with ``raw``, the unmodified UE5M3 bytes (0 = immaterial in the padding rows)."""
 
     tiles, atoms = (rows + 127) // 128, k // 64
-    out = np.full((tiles, atoms, 512), 0x78 if raw else 0x38, np.uint8)
+    out = np.full((tiles, atoms, 512), 0 if raw else 0x38, np.uint8)
     group = block if two_d else 1
     for r in range(rows):
         tile, r1, r0 = r // 128, (r % 128) // 32, r % 32

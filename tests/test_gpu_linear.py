@@ -204,6 +204,60 @@ def test_inference_lifecycle_training_replay():
     assert outputs[2].shape == (32, 64) and torch.isfinite(outputs[2].float()).all()
 
 
+def test_scale_byte_histograms_against_the_oracle(monkeypatch):
+    """Block-scale code counts as a by-product of the operand quantizers (read from the scale
+    bytes, not from the tensors) equal a numpy count of the oracle's scale codes: forward X of a
+    squared-ReLU layer (with all-zero blocks), the 2-D weight tiles, dY, and the two operands
+    blocked along the tokens; B = 16 and 32."""
+
+    monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+    from ue5m3_fp4.recipe import UE5M3Recipe
+
+    for block in (16, 32):
+        recipe = UE5M3Recipe.proposed()
+        if block == 32:
+            recipe = UE5M3Recipe.from_dict({**recipe.to_dict(), "block_size": 32, "name": "b32"})
+        tokens, in_f, out_f = 192, 256, 128
+        name = "layers.47.mixer.down_proj"
+        layer = _layer(in_f, out_f, bias=False, name=name, recipe=recipe, seed=block)
+        layer.capture_scale_histograms()
+        layer.scale_state.begin_step(1)
+        g = torch.Generator().manual_seed(block)
+        x = torch.relu(torch.randn(tokens, in_f, generator=g)).square()
+        x[:, 64:64 + block] = 0.0       # all-zero blocks along the features ...
+        x[32:64, 7] = 0.0               # ... and along the tokens
+        x = x.to(torch.bfloat16).cuda().requires_grad_(True)
+        dy = (1e-4 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16).cuda()
+        layer(x).backward(dy)
+        got = {key: value.cpu().numpy() for key, value in layer.scale_histograms().items()}
+        assert sorted(got) == ["activation", "activation_along_rows", "upstream_gradient", "weight",
+                               "weight_along_rows", "wgrad_upstream_gradient_along_rows"]
+        xh, wh, dyh = x.detach().float().cpu(), layer.weight.detach().float().cpu(), dy.float().cpu()
+        ax, aw, ady = float(xh.abs().max()), float(wh.abs().max()), float(dyh.abs().max())
+        t_wgrad = recipe.scale_target_for("wgrad_upstream_gradient", name)
+
+        def count(tensor, blocking, amax, target=448.0):
+            q = oracle_quantize(tensor, block=block, blocking=blocking, amax=amax, target=target)
+            codes = q["scale_codes"].astype(np.int64).copy()
+            codes[q["block_amax"] == 0] = 0       # bin 0: blocks whose elements are all zero
+            return np.bincount(codes.reshape(-1), minlength=256)
+
+        assert np.array_equal(got["activation"], count(xh, o.BLOCK_ROW, ax))
+        assert np.array_equal(got["activation_along_rows"], count(xh, o.BLOCK_COL, ax))
+        assert np.array_equal(got["weight"], count(wh, o.BLOCK_2D, aw))
+        assert np.array_equal(got["weight_along_rows"], count(wh, o.BLOCK_2D, aw))
+        assert np.array_equal(got["upstream_gradient"], count(dyh, o.BLOCK_ROW, ady))
+        assert np.array_equal(got["wgrad_upstream_gradient_along_rows"], count(dyh, o.BLOCK_COL, ady, t_wgrad))
+        assert got["activation"][0] >= tokens and got["activation_along_rows"][0] >= 32 // block
+        # a second step accumulates
+        layer.scale_state.begin_step(2)
+        layer.weight.grad = None
+        layer(x).backward(dy)
+        assert np.array_equal(layer.scale_histograms()["weight"].cpu().numpy(), 2 * got["weight"])
+        layer.capture_scale_histograms(False)
+        assert layer.scale_histograms() == {}
+
+
 def test_packed_weight_file_feeds_the_frozen_inference_path(tmp_path, monkeypatch):
     """export_packed_weight / load_packed_weight: the weight of a frozen layer goes to a packed
     file (0.5625 byte per element) and comes back as the forward operand; outputs are identical

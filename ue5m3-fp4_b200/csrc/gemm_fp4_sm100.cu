@@ -792,7 +792,7 @@ __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales, int64_t r
         const int64_t ka = atom % k_atoms, tile = atom / k_atoms;
         const int r0 = word >> 2, r1 = word & 3;
         const int64_t row = tile * 128 + r1 * 32 + r0;
-        uint32_t packed = 0x38383838u, raw = 0x78787878u;
+        uint32_t packed = 0x38383838u, raw = 0u;   // rows beyond the operand: 1.0 for the tensor core, 0 = immaterial in the raw atoms
         if (row < rows) {
             packed = raw = 0u;
             const uint8_t* src = scales + (row / row_group) * kblocks;

@@ -101,9 +101,54 @@ __global__ void __launch_bounds__(256) place_row_windows_kernel(const PlaceArgs 
     place_rows(args.op[1], args.k_atoms, warp_global, warps_total, lane);
 }
 
+// ---------------------------------------------------------------------------------------
+// Histogram of an operand's UE5M3 block-scale bytes, read from its raw scale atoms (1/16 byte
+// per element: the tensor itself is not touched again).  Bin b counts the blocks whose scale
+// byte is b; bin 0 counts blocks whose elements are all zero.  One shared-memory histogram per
+// CTA, flushed with one atomic per non-empty bin.  The device-side counterpart of the
+// block-scale diagnostics of reproduce/scale_target/capture_scale_target_histograms.py:257-366
+// of the reference (block count, zero blocks, saturated blocks, the code distribution).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) scale_byte_histogram_kernel(const uint32_t* __restrict__ raw, int64_t rows,
+                                                                   int64_t k_atoms, int block, int row_group,
+                                                                   unsigned long long* __restrict__ histogram) {
+    __shared__ unsigned int bins[256];
+    bins[threadIdx.x] = 0u;
+    __syncthreads();
+    const int64_t total = ((rows + 127) / 128) * k_atoms * 128;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int word = (int)(i % 128);                 // r0 * 4 + r1
+        const int64_t tile = (i / 128) / k_atoms;
+        const int64_t row = tile * 128 + (word & 3) * 32 + (word >> 2);
+        if (row >= rows || (row % row_group) != 0) continue;   // B x B tiles: one count per tile, not per row
+        const uint32_t bytes = __ldg(raw + i);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+            if (block == 32 && (kb & 1)) continue;       // a 32-wide block fills two 16-wide slots
+            atomicAdd(&bins[(bytes >> (8 * kb)) & 0xFFu], 1u);
+        }
+    }
+    __syncthreads();
+    if (bins[threadIdx.x]) atomicAdd(histogram + threadIdx.x, (unsigned long long)bins[threadIdx.x]);
+}
+
 }  // namespace ue5m3
 
 using namespace ue5m3;
+
+extern "C" int ue5m3_scale_byte_histogram(const uint8_t* sf_raw, int64_t rows, int64_t K, int block, int two_d,
+                                          unsigned long long* histogram_dev, void* stream_v) {
+    if (!sf_raw || !histogram_dev || rows <= 0 || K <= 0) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (block != 16 && block != 32) return UE5M3_ERR_BLOCK_SIZE;
+    if (K % 64) return UE5M3_ERR_K_NOT_DIVISIBLE;
+    if (((uintptr_t)sf_raw % 4) || ((uintptr_t)histogram_dev % 8)) return UE5M3_ERR_ALIGNMENT;
+    const int64_t total = ((rows + 127) / 128) * (K / 64) * 128;
+    const int64_t want = (total + 255) / 256;
+    const int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    scale_byte_histogram_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        reinterpret_cast<const uint32_t*>(sf_raw), rows, K / 64, block, two_d ? block : 1, histogram_dev);
+    return check_launch();
+}
 
 extern "C" int ue5m3_place_row_windows(uint8_t* a_sf, const uint8_t* a_sf_raw, int* a_record, int64_t a_rows,
                                        int a_shift, uint8_t* b_sf, const uint8_t* b_sf_raw, int* b_record,

@@ -92,6 +92,8 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32
     lib.ue5m3_gemm_fp4.argtypes = [p, p, p, p, i64, i64, i64, i32, i32, p, p, p, f32, p, i32, p, i32, i64, p, p, p, p]
+    lib.ue5m3_scale_byte_histogram.restype = i32
+    lib.ue5m3_scale_byte_histogram.argtypes = [p, i64, i64, i32, i32, p, p]
     lib.ue5m3_place_row_windows.restype = i32
     lib.ue5m3_place_row_windows.argtypes = [p, p, p, i64, i32, p, p, p, i64, i32, i64, p]
     lib.ue5m3_test_e2m1_cvt.restype = i32

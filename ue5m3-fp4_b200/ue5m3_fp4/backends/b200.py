@@ -690,6 +690,28 @@ def place_row_windows(a: Fp4Operand | None, b: Fp4Operand | None) -> None:
         op.placed = True
 
 
+def scale_byte_histogram(operand: Fp4Operand, *, block_size: int, two_dimensional: bool = False,
+                         out: Tensor | None = None) -> Tensor:
+    """256 int64 counters: how many blocks of the operand carry each UE5M3 scale byte (bin 0: blocks
+    whose elements are all zero; byte 0xF7: saturated).  Accumulates into ``out`` when given.  Reads
+    only the operand's raw scale atoms.  The device-side form of the block-scale diagnostics of
+    reproduce/scale_target/capture_scale_target_histograms.py:257-366 of the reference."""
+
+    if operand.raw_scale_factors is None:
+        raise ValueError("the operand carries no raw scale atoms")
+    device = operand.codes.device
+    if out is None:
+        out = torch.zeros(256, dtype=torch.int64, device=device)
+    elif out.dtype is not torch.int64 or out.numel() != 256 or out.device != device or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int64 tensor of 256 counters on the operand's device")
+    with torch.cuda.device(device):
+        status = _native.load().ue5m3_scale_byte_histogram(
+            operand.raw_scale_factors.data_ptr(), operand.rows, operand.k, block_size, int(two_dimensional),
+            out.data_ptr(), _native.stream_ptr(device))
+    _native.check(status, "ue5m3_scale_byte_histogram")
+    return out
+
+
 _window_log: list | None = None
 
 
@@ -1026,6 +1048,7 @@ __all__ = [
     "quantize_fp4_operand",
     "new_window_record",
     "place_row_windows",
+    "scale_byte_histogram",
     "log_window_records",
     "window_log_summary",
     "poll_gemm_status",

@@ -148,6 +148,7 @@ class _OperandPlan:
 
         self.recipe = owner.recipe
         self.name = owner.module_name
+        self.owner = owner
         self.block = owner.recipe.block_size
         # FP4 tensor cores for the probe-matched backend unless the environment asks for the
         # BF16-issue kernel; the torch control always multiplies encoded bf16 operands.
@@ -188,11 +189,17 @@ def _encode_k_major(
         blocking = b200.BLOCK_COL if reduce_over_rows else b200.BLOCK_ROW
     if plan.path == "fp4":
         # one binade of headroom: a held amax may lag the data between refreshes
-        return b200.quantize_fp4_operand(
+        operand = b200.quantize_fp4_operand(
             tensor, block_size=plan.block, blocking=blocking, transposed=reduce_over_rows,
             tensor_amax=reference.reshape(1), scale_target=plan.target(role), rounding=rounding,
             random_bits=bits, shift_headroom=1, hadamard=hadamard,
         )
+        histograms = plan.owner.__dict__.get("_scale_histograms")
+        if histograms is not None:  # opt-in diagnostics: block-scale code counts per operand role
+            key = f"{plan.recipe.normalize_role(role).value}{'_along_rows' if reduce_over_rows else ''}"
+            histograms[key] = b200.scale_byte_histogram(operand, block_size=plan.block, two_dimensional=two_dimensional,
+                                                        out=histograms.get(key))
+        return operand
     if hadamard:
         raise NotImplementedError(
             "the Hadamard-transformed weight-gradient operands exist on the FP4 tensor-core path only "
@@ -512,6 +519,20 @@ class UE5M3Linear(torch.nn.Module):
         return (weight.data_ptr(), weight._version, tuple(weight.shape), weight.dtype,
                 self._inference["frozen_weights"].get("forward.w"), plan.path, plan.block,
                 self.recipe.two_dimensional_weights)
+
+    def capture_scale_histograms(self, enable: bool = True) -> None:
+        """Start (or stop and drop) counting the UE5M3 block-scale bytes of every operand this
+        layer quantizes on the FP4 path: ``scale_histograms()`` then maps an operand role
+        (``activation``, ``weight``, ``upstream_gradient``, and with ``_along_rows`` appended the
+        operands blocked along the tokens for the weight-gradient product) to 256 counters.  The
+        counts come from the scale bytes the quantizers write anyway; the tensors are not read
+        again.  Device-side form of reproduce/scale_target/capture_scale_target_histograms.py of
+        the reference."""
+
+        self.__dict__["_scale_histograms"] = {} if enable else None
+
+    def scale_histograms(self) -> dict[str, torch.Tensor]:
+        return dict(self.__dict__.get("_scale_histograms") or {})
 
     def export_packed_weight(self, path) -> None:
         """Write this layer's weight, quantized with its FROZEN amax, as a packed FP4 tensor file
