@@ -73,16 +73,19 @@ struct Fp4Params {
     // (window_place.cu) carry an extra exponent there; the epilogue multiplies by 2^(a[row] + b[col]).
     const int* rec_a;
     const int* rec_b;
-    const int* row_shift_a;  // set inside the kernel: null unless the record says that rows were placed
-    const int* row_shift_b;
 };
 
-// the kernel's parameters with the per-row exponent tables resolved from the records
-__device__ __forceinline__ Fp4Params resolve_row_shifts(const Fp4Params& p) {
-    Fp4Params q = p;
-    q.row_shift_a = (p.rec_a && __ldg(p.rec_a + kRecPlaced) > 0) ? rec_row_shift(p.rec_a, p.M) : nullptr;
-    q.row_shift_b = (p.rec_b && __ldg(p.rec_b + kRecPlaced) > 0) ? rec_row_shift(p.rec_b, p.N) : nullptr;
-    return q;
+// per-row exponent tables of the operands: null unless the record says that rows were placed
+struct RowShifts {
+    const int* a;
+    const int* b;
+};
+
+__device__ __forceinline__ RowShifts resolve_row_shifts(const Fp4Params& p) {
+    RowShifts shifts;
+    shifts.a = (p.rec_a && __ldg(p.rec_a + kRecPlaced) > 0) ? rec_row_shift(p.rec_a, p.M) : nullptr;
+    shifts.b = (p.rec_b && __ldg(p.rec_b + kRecPlaced) > 0) ? rec_row_shift(p.rec_b, p.N) : nullptr;
+    return shifts;
 }
 
 struct __align__(8) Fp4Barriers {
@@ -123,9 +126,10 @@ __host__ __device__ constexpr uint32_t make_idesc_fp4(int m, int n) {
 
 // Epilogue arithmetic and stores of one thread: 128 accumulator values of one output row
 // (columns [tile_n * 256 + h * 128, + 128)): rescale by 2^shift, snap, alpha, bias, cast.
-__device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t (&v)[4][32], long long row,
-                                              int tile_n, int h, float alpha) {
-    const float row_factor = p.row_shift_a ? __fmul_rn(p.rescale, exp2_int(__ldg(p.row_shift_a + row))) : p.rescale;
+template <bool kColumnShifts>
+__device__ __forceinline__ void fp4_store_row_impl(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
+                                                   long long row, int tile_n, int h, float alpha) {
+    const float row_factor = shifts.a ? __fmul_rn(p.rescale, exp2_int(__ldg(shifts.a + row))) : p.rescale;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
@@ -134,9 +138,9 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             float x = __fmul_rn(__uint_as_float(v[chunk][i]), row_factor);
-            if (p.row_shift_b && col0 + i < p.N) x = __fmul_rn(x, exp2_int(__ldg(p.row_shift_b + col0 + i)));
+            if (kColumnShifts && col0 + i < p.N) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + i)));
             if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
-            if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
+            x = __fmul_rn(x, alpha);   // alpha is 1 when the caller gave none: an exact no-op
             c[i] = x;
         }
         if (p.bias) {
@@ -188,6 +192,20 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
     }
 }
 
+// out of line: the rare path must not cost the common one registers
+__device__ __noinline__ void fp4_store_row_column_shifts(const Fp4Params& p, const RowShifts shifts,
+                                                         const uint32_t (&v)[4][32], long long row, int tile_n, int h,
+                                                         float alpha) {
+    fp4_store_row_impl<true>(p, shifts, v, row, tile_n, h, alpha);
+}
+
+__device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
+                                              long long row, int tile_n, int h, float alpha) {
+    // placed operand rows of B (= output columns) are rare: keep their per-column factor out of the common path
+    if (shifts.b) fp4_store_row_column_shifts(p, shifts, v, row, tile_n, h, alpha);
+    else fp4_store_row_impl<false>(p, shifts, v, row, tile_n, h, alpha);
+}
+
 // The same epilogue arithmetic for one warp's 32 rows x 128 columns with BF16 output, stored
 // through a per-warp 32 x 128-byte staging buffer so that every store instruction writes four
 // full 128-byte lines (lane = 16 bytes of a row) instead of 16 bytes in each of 32 rows.
@@ -195,11 +213,12 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const uint32_t
 // Requires the whole 128-column half inside N, ldo % 8 == 0 and a 16-byte aligned base.
 constexpr uint32_t kStageBytesPerWarp = 32 * 128;
 
-__device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const uint32_t (&v)[4][32],
-                                                           long long row0, int tile_n, int h, float alpha,
-                                                           unsigned char* stage, int lane) {
+template <bool kColumnShifts>
+__device__ __forceinline__ void fp4_store_rows_staged_bf16_impl(const Fp4Params& p, const RowShifts shifts,
+                                                                const uint32_t (&v)[4][32], long long row0, int tile_n,
+                                                                int h, float alpha, unsigned char* stage, int lane) {
     float row_factor = p.rescale;
-    if (p.row_shift_a && row0 + lane < p.M) row_factor = __fmul_rn(row_factor, exp2_int(__ldg(p.row_shift_a + row0 + lane)));
+    if (shifts.a && row0 + lane < p.M) row_factor = __fmul_rn(row_factor, exp2_int(__ldg(shifts.a + row0 + lane)));
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + pass * 64;
@@ -210,9 +229,9 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, c
             for (int e = 0; e < 8; ++e) {
                 const int idx = pass * 64 + c * 8 + e;
                 float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), row_factor);
-                if (p.row_shift_b) x = __fmul_rn(x, exp2_int(__ldg(p.row_shift_b + col0 + c * 8 + e)));
+                if (kColumnShifts) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + c * 8 + e)));
                 if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
-                if (alpha_enabled(p.alpha)) x = __fmul_rn(x, alpha);
+                x = __fmul_rn(x, alpha);   // alpha is 1 when the caller gave none: an exact no-op
                 if (p.bias) {
                     const int col = col0 + c * 8 + e;
                     const float bv = p.bias_dtype == UE5M3_DTYPE_BF16
@@ -239,6 +258,19 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, c
         }
         __syncwarp();
     }
+}
+
+__device__ __noinline__ void fp4_store_rows_staged_column_shifts(const Fp4Params& p, const RowShifts shifts,
+                                                                 const uint32_t (&v)[4][32], long long row0, int tile_n,
+                                                                 int h, float alpha, unsigned char* stage, int lane) {
+    fp4_store_rows_staged_bf16_impl<true>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
+}
+
+__device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const RowShifts shifts,
+                                                           const uint32_t (&v)[4][32], long long row0, int tile_n,
+                                                           int h, float alpha, unsigned char* stage, int lane) {
+    if (shifts.b) fp4_store_rows_staged_column_shifts(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
+    else fp4_store_rows_staged_bf16_impl<false>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
 }
 
 // tile index -> (tile_m, tile_n): groups of 8 tile rows sweep the tile columns together
@@ -428,7 +460,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;          // TMEM lane quadrant
         const int h = (warp - 2) >> 2;   // column half of the tile
         const float alpha = alpha_value(p.alpha);
-        const Fp4Params pq = resolve_row_shifts(p);
+        const RowShifts shifts = resolve_row_shifts(p);
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             int tile_m, tile_n;
@@ -448,7 +480,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
             const long long row = (long long)tile_m * kFM + q * 32 + lane;
             if (row >= p.M) continue;
-            fp4_store_row(pq, v, row, tile_n, h, alpha);
+            fp4_store_row(p, shifts, v, row, tile_n, h, alpha);
         }
     }
 
@@ -725,7 +757,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int q = warp & 3;
         const int h = (warp - 2) >> 2;
         const float alpha = alpha_value(p.alpha);
-        const Fp4Params pq = resolve_row_shifts(p);
+        const RowShifts shifts = resolve_row_shifts(p);
         const uint32_t tmem_empty_leader = map_to_cta(smem_u32(&bars->tmem_empty), 0);
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
@@ -748,13 +780,13 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const bool staged = p.out_dtype == UE5M3_DTYPE_BF16 && (p.ldo % 8) == 0 &&
                                 ((uintptr_t)p.out % 16) == 0 && tile_n * kFN + (h + 1) * (kFN / 2) <= p.N;
             if (staged) {
-                fp4_store_rows_staged_bf16(pq, v, row0, tile_n, h, alpha,
+                fp4_store_rows_staged_bf16(p, shifts, v, row0, tile_n, h, alpha,
                                            stage_base + (warp - 2) * kStageBytesPerWarp, lane);
                 continue;
             }
             const long long row = row0 + lane;
             if (row >= p.M) continue;
-            fp4_store_row(pq, v, row, tile_n, h, alpha);
+            fp4_store_row(p, shifts, v, row, tile_n, h, alpha);
         }
     }
 
@@ -948,7 +980,7 @@ extern "C" int ue5m3_gemm_fp4(const uint8_t* a_codes, const uint8_t* a_sf, const
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
     p.sfa = a_sf; p.sfb = b_sf;
-    p.rec_a = a_record; p.rec_b = b_record; p.row_shift_a = nullptr; p.row_shift_b = nullptr;
+    p.rec_a = a_record; p.rec_b = b_record;
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
     const int64_t tiles = tiles_m * tiles_n;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
