@@ -192,17 +192,10 @@ __device__ __forceinline__ void fp4_store_row_impl(const Fp4Params& p, const Row
     }
 }
 
-// out of line: the rare path must not cost the common one registers
-__device__ __noinline__ void fp4_store_row_column_shifts(const Fp4Params& p, const RowShifts shifts,
-                                                         const uint32_t (&v)[4][32], long long row, int tile_n, int h,
-                                                         float alpha) {
-    fp4_store_row_impl<true>(p, shifts, v, row, tile_n, h, alpha);
-}
-
 __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
                                               long long row, int tile_n, int h, float alpha) {
     // placed operand rows of B (= output columns) are rare: keep their per-column factor out of the common path
-    if (shifts.b) fp4_store_row_column_shifts(p, shifts, v, row, tile_n, h, alpha);
+    if (shifts.b) fp4_store_row_impl<true>(p, shifts, v, row, tile_n, h, alpha);
     else fp4_store_row_impl<false>(p, shifts, v, row, tile_n, h, alpha);
 }
 
@@ -260,16 +253,10 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16_impl(const Fp4Params&
     }
 }
 
-__device__ __noinline__ void fp4_store_rows_staged_column_shifts(const Fp4Params& p, const RowShifts shifts,
-                                                                 const uint32_t (&v)[4][32], long long row0, int tile_n,
-                                                                 int h, float alpha, unsigned char* stage, int lane) {
-    fp4_store_rows_staged_bf16_impl<true>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
-}
-
 __device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const RowShifts shifts,
                                                            const uint32_t (&v)[4][32], long long row0, int tile_n,
                                                            int h, float alpha, unsigned char* stage, int lane) {
-    if (shifts.b) fp4_store_rows_staged_column_shifts(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
+    if (shifts.b) fp4_store_rows_staged_bf16_impl<true>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
     else fp4_store_rows_staged_bf16_impl<false>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
 }
 

@@ -37,6 +37,15 @@ struct PlaceArgs {
     int k_atoms;          // K / 64
 };
 
+// A UE5M3 byte as a position on the scale of NORMAL codes (8 per binade, 0x78 = 1.0): bytes
+// 8..0xF7 are that already; the subnormal bytes 1..7 stand for m * 2^-17, each of which is a
+// normal number with three fraction bits a few binades lower (1 -> 2^-17, 3 -> 1.5 * 2^-16, ...),
+// so they continue the scale below zero.  UE4M3 = this position minus (8 + shift) * 8.
+__device__ __forceinline__ int normal_position(uint32_t byte) {
+    constexpr int kSubnormal[8] = {0, -16, -8, -4, 0, 2, 4, 6};
+    return byte >= 8u ? (int)byte : kSubnormal[byte];
+}
+
 __device__ __forceinline__ void place_rows(const PlaceOperand& o, int k_atoms, int warp_global, int warps_total,
                                            int lane) {
     if (!o.rec || __ldg(o.rec + kRecFlagged) == 0) return;
@@ -45,16 +54,16 @@ __device__ __forceinline__ void place_rows(const PlaceOperand& o, int k_atoms, i
     for (int row = warp_global; row < o.rows; row += warps_total) {
         if (flags[row] == 0) continue;
         const int64_t base = ((int64_t)(row >> 7) * k_atoms) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-        // largest and smallest scale byte of the row's non-zero blocks
-        uint32_t top = 0u, bottom = 0xFFu;
+        // largest and smallest scale of the row's non-zero blocks
+        int top = -1000, bottom = 1000;
         for (int ka = lane; ka < k_atoms; ka += 32) {
             const uint32_t word = *reinterpret_cast<const uint32_t*>(o.raw + base + (int64_t)ka * 512);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const uint32_t byte = (word >> (8 * b)) & 0xFFu;
                 if (byte != 0u) {
-                    top = max(top, byte);
-                    bottom = min(bottom, byte);
+                    top = max(top, normal_position(byte));
+                    bottom = min(bottom, normal_position(byte));
                 }
             }
         }
@@ -63,12 +72,12 @@ __device__ __forceinline__ void place_rows(const PlaceOperand& o, int k_atoms, i
             top = max(top, __shfl_xor_sync(0xFFFFFFFFu, top, d));
             bottom = min(bottom, __shfl_xor_sync(0xFFFFFFFFu, bottom, d));
         }
-        if (top == 0u) continue;  // nothing but zero blocks
-        // smallest shift that brings the largest byte to 0x7E or below: byte - ((8 + s) << 3) <= 0x7E
-        int shift = ((int)top - 0x7E + 7) >> 3;   // ceil((top - 0x7E) / 8), also for negative values
+        if (top == -1000) continue;  // nothing but zero blocks
+        // smallest shift that brings the largest scale to 0x7E or below: top - ((8 + s) << 3) <= 0x7E
+        int shift = (top - 0x7E + 7) >> 3;   // ceil((top - 0x7E) / 8), also for negative values
         shift -= 8;
         const int rebias = (8 + shift) << 3;
-        if ((int)bottom - rebias < 8) {
+        if (bottom - rebias < 8) {
             // the row's own scales span more than the window: recompute it
             if (lane == 0) {
                 const int slot = atomicAdd(o.rec + kRecListed, 1);
@@ -82,7 +91,7 @@ __device__ __forceinline__ void place_rows(const PlaceOperand& o, int k_atoms, i
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const uint32_t byte = (word >> (8 * b)) & 0xFFu;
-                out |= (byte == 0u ? 0x38u : (uint32_t)((int)byte - rebias)) << (8 * b);
+                out |= (byte == 0u ? 0x38u : (uint32_t)(normal_position(byte) - rebias)) << (8 * b);
             }
             *reinterpret_cast<uint32_t*>(o.sf + base + (int64_t)ka * 512) = out;
         }
