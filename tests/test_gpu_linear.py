@@ -324,7 +324,7 @@ def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monk
 
     import ue5m3_fp4.nn.linear as linear_module
 
-    tokens, in_f, out_f = 512, 1024, 384
+    tokens, in_f, out_f = 1024, 2048, 384
     results = {}
     for mode in ("1", "0"):
         monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
