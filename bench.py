@@ -583,8 +583,7 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
                 logits = wrapped(ids)
                 loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels)
                 loss.backward()
-            if sync:
-                optimizer.step()
+            optimizer.step()   # also in the run without gradient all-reduce, so that the two differ by it alone
             optimizer.zero_grad(set_to_none=True)
 
         def timed(indices, sync: bool = True) -> float:

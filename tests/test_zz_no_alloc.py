@@ -45,6 +45,29 @@ def test_static_scratch_amax_equals_caller_scratch_amax_twice_in_a_row():
         assert got == expected == tensor.float().abs().max().item()
 
 
+def test_static_scratch_amax_allocates_no_device_memory():
+    """What the entry point is for: neither the driver's free-memory figure nor torch's
+    allocator moves across calls (after the first call on the device, which only looks up the
+    address of the library's own array)."""
+
+    from ue5m3_fp4 import _native as native
+
+    lib = native.load()
+    x = torch.randn(1 << 22, device="cuda")
+    out = torch.zeros((), dtype=torch.float32, device="cuda")
+    stream = native.stream_ptr(x.device)
+    native.check(lib.ue5m3_amax_static(x.data_ptr(), 1, x.numel(), out.data_ptr(), stream), "ue5m3_amax_static")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    allocated_before, reserved_before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        native.check(lib.ue5m3_amax_static(x.data_ptr(), 1, x.numel(), out.data_ptr(), stream), "ue5m3_amax_static")
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before   # nothing was taken from the device
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == (allocated_before, reserved_before)
+    assert out.item() == x.abs().max().item()
+
+
 def test_static_scratch_amax_rejects_oversized_and_bad_arguments():
     from ue5m3_fp4 import _native as native
 

@@ -138,7 +138,11 @@ static int amax_grid(int dtype, int64_t n) {
 
 using namespace ue5m3;
 
-// Device address of the static scratch on the current device, resolved on first use.
+// Device address of the static scratch on the current device, resolved on first use.  The
+// table is written without a lock: two threads that race on a device's first call both look
+// the address up and both store the same value, so the worst case is one redundant lookup.
+// It is keyed by the CURRENT device, which therefore has to be the stream's device on every
+// call, not only on the first.
 static int static_scratch_for_device(AmaxScratch** out) {
     static AmaxScratch* cache[kMaxDevices] = {nullptr};
     int device = -1;
