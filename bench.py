@@ -832,6 +832,23 @@ def run_case(args) -> None:
         alpha = b200.encoded_global_alpha(amax_a, amax_b, TARGET, TARGET)
         for _ in range(args.steps):
             b200.gemm_fp4_operands(qa, qb, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+    elif args.case == "fallback-small":
+        # squared-ReLU activations at B=16: some block scales leave the tensor core's window, so the
+        # row placement and the recomputation pass have work to do (X 4096x8192, W 2048x8192)
+        m, n, kk = 4096, 2048, 8192
+        gd = torch.Generator(device=device).manual_seed(0)
+        a = torch.relu(torch.randn(m, kk, device=device, generator=gd)).square_().to(torch.bfloat16)
+        b = (0.02 * torch.randn(n, kk, device=device, generator=gd)).to(torch.bfloat16)
+        amax_a, amax_b = b200.tensor_amax(a).reshape(1), b200.tensor_amax(b).reshape(1)
+        alpha = b200.EpilogueAlpha.of(amax_a, amax_b, TARGET, TARGET)
+        for _ in range(args.steps):
+            qa = b200.quantize_fp4_operand(a, block_size=BLOCK, blocking=b200.BLOCK_ROW, transposed=False,
+                                           tensor_amax=amax_a, scale_target=TARGET, shift_headroom=1)
+            qb = b200.quantize_fp4_operand(b, block_size=BLOCK, blocking=b200.BLOCK_2D, transposed=False,
+                                           tensor_amax=amax_b, scale_target=TARGET, shift_headroom=1)
+            b200.gemm_fp4_operands(qa, qb, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        print("flagged rows", qa.window_counts(), "placement: listed", len(qa.placement()[0]), "placed", len(qa.placement()[1]))
     elif args.case == "linear-step":
         # forward + backward of one UE5M3Linear of the benchmark shape (launch-list captures)
         from ue5m3_fp4.nn import UE5M3Linear
@@ -877,7 +894,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize", "linear-step"],
+    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize", "linear-step", "fallback-small"],
                         help="run one small kernel case for a profiler capture instead of the benchmark")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
