@@ -96,6 +96,7 @@ struct __align__(8) Fp4Barriers {
     unsigned long long tmem_empty;
     uint32_t tmem_base;
     int abort_flag;
+    Fp4Params params;   // a copy that out-of-line code can point to
 };
 
 // D[tmem] (+)= A[smem] * B[smem] with per-16 block scales read from TMEM.
@@ -126,10 +127,10 @@ __host__ __device__ constexpr uint32_t make_idesc_fp4(int m, int n) {
 
 // Epilogue arithmetic and stores of one thread: 128 accumulator values of one output row
 // (columns [tile_n * 256 + h * 128, + 128)): rescale by 2^shift, snap, alpha, bias, cast.
-template <bool kColumnShifts>
-__device__ __forceinline__ void fp4_store_row_impl(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
-                                                   long long row, int tile_n, int h, float alpha) {
-    const float row_factor = shifts.a ? __fmul_rn(p.rescale, exp2_int(__ldg(shifts.a + row))) : p.rescale;
+template <bool kShifts>
+__device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
+                                              long long row, int tile_n, int h, float alpha) {
+    const float row_factor = (kShifts && shifts.a) ? __fmul_rn(p.rescale, exp2_int(__ldg(shifts.a + row))) : p.rescale;
 #pragma unroll
     for (int chunk = 0; chunk < 4; ++chunk) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + chunk * 32;
@@ -138,7 +139,7 @@ __device__ __forceinline__ void fp4_store_row_impl(const Fp4Params& p, const Row
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             float x = __fmul_rn(__uint_as_float(v[chunk][i]), row_factor);
-            if (kColumnShifts && col0 + i < p.N) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + i)));
+            if (kShifts && shifts.b && col0 + i < p.N) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + i)));
             if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
             x = __fmul_rn(x, alpha);   // alpha is 1 when the caller gave none: an exact no-op
             c[i] = x;
@@ -192,13 +193,6 @@ __device__ __forceinline__ void fp4_store_row_impl(const Fp4Params& p, const Row
     }
 }
 
-__device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const RowShifts shifts, const uint32_t (&v)[4][32],
-                                              long long row, int tile_n, int h, float alpha) {
-    // placed operand rows of B (= output columns) are rare: keep their per-column factor out of the common path
-    if (shifts.b) fp4_store_row_impl<true>(p, shifts, v, row, tile_n, h, alpha);
-    else fp4_store_row_impl<false>(p, shifts, v, row, tile_n, h, alpha);
-}
-
 // The same epilogue arithmetic for one warp's 32 rows x 128 columns with BF16 output, stored
 // through a per-warp 32 x 128-byte staging buffer so that every store instruction writes four
 // full 128-byte lines (lane = 16 bytes of a row) instead of 16 bytes in each of 32 rows.
@@ -206,12 +200,12 @@ __device__ __forceinline__ void fp4_store_row(const Fp4Params& p, const RowShift
 // Requires the whole 128-column half inside N, ldo % 8 == 0 and a 16-byte aligned base.
 constexpr uint32_t kStageBytesPerWarp = 32 * 128;
 
-template <bool kColumnShifts>
-__device__ __forceinline__ void fp4_store_rows_staged_bf16_impl(const Fp4Params& p, const RowShifts shifts,
-                                                                const uint32_t (&v)[4][32], long long row0, int tile_n,
-                                                                int h, float alpha, unsigned char* stage, int lane) {
+template <bool kShifts>
+__device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const RowShifts shifts,
+                                                           const uint32_t (&v)[4][32], long long row0, int tile_n,
+                                                           int h, float alpha, unsigned char* stage, int lane) {
     float row_factor = p.rescale;
-    if (shifts.a && row0 + lane < p.M) row_factor = __fmul_rn(row_factor, exp2_int(__ldg(shifts.a + row0 + lane)));
+    if (kShifts && shifts.a && row0 + lane < p.M) row_factor = __fmul_rn(row_factor, exp2_int(__ldg(shifts.a + row0 + lane)));
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
         const int col0 = tile_n * kFN + h * (kFN / 2) + pass * 64;
@@ -222,7 +216,7 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16_impl(const Fp4Params&
             for (int e = 0; e < 8; ++e) {
                 const int idx = pass * 64 + c * 8 + e;
                 float x = __fmul_rn(__uint_as_float(v[idx >> 5][idx & 31]), row_factor);
-                if (kColumnShifts) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + c * 8 + e)));
+                if (kShifts && shifts.b) x = __fmul_rn(x, exp2_int(__ldg(shifts.b + col0 + c * 8 + e)));
                 if (p.snap) x = __fmul_rn(rint_rne(__fmul_rn(x, 1024.0f)), 0.0009765625f);
                 x = __fmul_rn(x, alpha);   // alpha is 1 when the caller gave none: an exact no-op
                 if (p.bias) {
@@ -253,11 +247,52 @@ __device__ __forceinline__ void fp4_store_rows_staged_bf16_impl(const Fp4Params&
     }
 }
 
-__device__ __forceinline__ void fp4_store_rows_staged_bf16(const Fp4Params& p, const RowShifts shifts,
-                                                           const uint32_t (&v)[4][32], long long row0, int tile_n,
-                                                           int h, float alpha, unsigned char* stage, int lane) {
-    if (shifts.b) fp4_store_rows_staged_bf16_impl<true>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
-    else fp4_store_rows_staged_bf16_impl<false>(p, shifts, v, row0, tile_n, h, alpha, stage, lane);
+// One epilogue warp's share of one tile: 32 accumulator rows x 128 columns out of TMEM (which is
+// released as soon as the values are in registers: `release`), then arithmetic and stores.
+// kShifts = true is the rare case that an operand has rows with a scale window of their own;
+// it lives in a function of its own (below) so that the common case keeps its registers.
+struct TileEpilogue {
+    uint32_t taddr;               // TMEM address of this warp's lanes and columns
+    long long row0;               // first output row of this warp
+    int rows_per_thread_valid;    // unused padding to keep the struct trivially copyable
+    int tile_n, h, lane;
+    float alpha;
+    unsigned char* stage;         // per-warp staging buffer, or null: direct stores
+    unsigned long long* release_local;   // mbarrier to arrive on after the TMEM reads (this CTA's) ...
+    uint32_t release_cluster;            // ... or its cluster address in the leader CTA (pair kernel); 0 = use local
+};
+
+template <bool kShifts>
+__device__ __forceinline__ void fp4_tile_epilogue(const Fp4Params& p, const RowShifts shifts, const TileEpilogue& t) {
+    uint32_t v[4][32];
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) tmem_load_32_async(t.taddr + chunk * 32, v[chunk]);
+    tmem_wait_ld();
+    tcgen05_fence_before();
+    __syncwarp();
+    if (t.lane == 0) {
+        if (t.release_cluster) mbar_arrive_cluster(t.release_cluster);
+        else mbar_arrive(t.release_local);
+    }
+    if (t.stage) {
+        fp4_store_rows_staged_bf16<kShifts>(p, shifts, v, t.row0, t.tile_n, t.h, t.alpha, t.stage, t.lane);
+        return;
+    }
+    const long long row = t.row0 + t.lane;
+    if (row < p.M) fp4_store_row<kShifts>(p, shifts, v, row, t.tile_n, t.h, t.alpha);
+}
+
+// everything by value or through shared memory: a reference to the kernel's parameters or to a
+// local struct would force a copy of them onto the caller's stack
+__device__ __noinline__ void fp4_tile_epilogue_with_row_shifts(const Fp4Params* params_in_shared, const int* shift_a,
+                                                               const int* shift_b, uint32_t taddr, long long row0,
+                                                               int tile_n, int h, int lane, float alpha,
+                                                               unsigned char* stage, unsigned long long* release_local,
+                                                               uint32_t release_cluster) {
+    TileEpilogue t;
+    t.taddr = taddr; t.row0 = row0; t.rows_per_thread_valid = 0; t.tile_n = tile_n; t.h = h; t.lane = lane;
+    t.alpha = alpha; t.stage = stage; t.release_local = release_local; t.release_cluster = release_cluster;
+    fp4_tile_epilogue<true>(*params_in_shared, RowShifts{shift_a, shift_b}, t);
 }
 
 // tile index -> (tile_m, tile_n): groups of 8 tile rows sweep the tile columns together
@@ -298,6 +333,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         mbar_init(&bars->tmem_full, 1);
         mbar_init(&bars->tmem_empty, kFEpilogueWarps);
         bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
+        bars->params = p;
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(&bars->tmem_base, kFTmemCols);
@@ -448,6 +484,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int h = (warp - 2) >> 2;   // column half of the tile
         const float alpha = alpha_value(p.alpha);
         const RowShifts shifts = resolve_row_shifts(p);
+        const bool has_shifts = shifts.a != nullptr || shifts.b != nullptr;
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             int tile_m, tile_n;
@@ -456,18 +493,18 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
-            uint32_t v[4][32];
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) tmem_load_32_async(taddr + chunk * 32, v[chunk]);
-            tmem_wait_ld();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty);
-
-            const long long row = (long long)tile_m * kFM + q * 32 + lane;
-            if (row >= p.M) continue;
-            fp4_store_row(p, shifts, v, row, tile_n, h, alpha);
+            TileEpilogue t;
+            t.taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
+            t.row0 = (long long)tile_m * kFM + q * 32;
+            t.rows_per_thread_valid = 0;
+            t.tile_n = tile_n; t.h = h; t.lane = lane; t.alpha = alpha;
+            t.stage = nullptr;
+            t.release_local = &bars->tmem_empty;
+            t.release_cluster = 0u;
+            if (has_shifts)
+                fp4_tile_epilogue_with_row_shifts(&bars->params, shifts.a, shifts.b, t.taddr, t.row0, t.tile_n, t.h, t.lane,
+                                                  t.alpha, t.stage, t.release_local, t.release_cluster);
+            else fp4_tile_epilogue<false>(p, shifts, t);
         }
     }
 
@@ -509,6 +546,7 @@ struct __align__(8) Fp4PairBarriers {
     unsigned long long tmem_empty;         // leader's: epilogue warps of both CTAs
     uint32_t tmem_base;
     int abort_flag;
+    Fp4Params params;                      // a copy that out-of-line code can point to
 };
 
 __device__ __forceinline__ void umma_fp4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -572,6 +610,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         mbar_init(&bars->tmem_full, 1);
         mbar_init(&bars->tmem_empty, 2 * kFEpilogueWarps);
         bars->abort_flag = (p.status && *((volatile int*)p.status) != 0) ? 1 : 0;
+        bars->params = p;
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc_pair(&bars->tmem_base, kFTmemCols);
@@ -745,6 +784,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int h = (warp - 2) >> 2;
         const float alpha = alpha_value(p.alpha);
         const RowShifts shifts = resolve_row_shifts(p);
+        const bool has_shifts = shifts.a != nullptr || shifts.b != nullptr;
         const uint32_t tmem_empty_leader = map_to_cta(smem_u32(&bars->tmem_empty), 0);
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
@@ -754,26 +794,20 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
-            uint32_t v[4][32];
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) tmem_load_32_async(taddr + chunk * 32, v[chunk]);
-            tmem_wait_ld();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tmem_empty_leader);
-
-            const long long row0 = (long long)tile_m * kPM + (long long)rank * 128 + q * 32;
             const bool staged = p.out_dtype == UE5M3_DTYPE_BF16 && (p.ldo % 8) == 0 &&
                                 ((uintptr_t)p.out % 16) == 0 && tile_n * kFN + (h + 1) * (kFN / 2) <= p.N;
-            if (staged) {
-                fp4_store_rows_staged_bf16(p, shifts, v, row0, tile_n, h, alpha,
-                                           stage_base + (warp - 2) * kStageBytesPerWarp, lane);
-                continue;
-            }
-            const long long row = row0 + lane;
-            if (row >= p.M) continue;
-            fp4_store_row(p, shifts, v, row, tile_n, h, alpha);
+            TileEpilogue t;
+            t.taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * (kFN / 2));
+            t.row0 = (long long)tile_m * kPM + (long long)rank * 128 + q * 32;
+            t.rows_per_thread_valid = 0;
+            t.tile_n = tile_n; t.h = h; t.lane = lane; t.alpha = alpha;
+            t.stage = staged ? stage_base + (warp - 2) * kStageBytesPerWarp : nullptr;
+            t.release_local = nullptr;
+            t.release_cluster = tmem_empty_leader;
+            if (has_shifts)
+                fp4_tile_epilogue_with_row_shifts(&bars->params, shifts.a, shifts.b, t.taddr, t.row0, t.tile_n, t.h, t.lane,
+                                                  t.alpha, t.stage, t.release_local, t.release_cluster);
+            else fp4_tile_epilogue<false>(p, shifts, t);
         }
     }
 
