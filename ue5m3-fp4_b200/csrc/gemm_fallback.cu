@@ -190,28 +190,27 @@ struct StageLoads {
     uint32_t byte[kItems];
 };
 
+// where a thread's items of the current tile live: the codes of (row, chunk) at issue 0 and the
+// row's raw scale byte of that chunk in atom 0; null for rows beyond the operand (and for the
+// last item of threads that have one item fewer)
+struct ItemSources {
+    const uint32_t* codes[kItems];
+    const uint8_t* scale[kItems];
+};
+
 // issues the global loads of one stage (they complete while the previous stage is decoded)
-__device__ __forceinline__ void load_stage(StageLoads& loads, const Params& p, const int (&item_row)[kItems], int issue,
-                                           int producer_thread) {
-    const int64_t k_atoms = p.K / 64;
+__device__ __forceinline__ void load_stage(StageLoads& loads, const ItemSources& src, int issue) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
-        const int item = producer_thread + i * (kProducerWarps * 32);
-        const int r = item >> 3, c = item & 7;        // r < kBM: A row, else B row
-        const int64_t row = item_row[i];              // operand row, -1 = beyond the operand (or no such item)
-        loads.word[i] = 0u;
-        loads.byte[i] = 0x78u;
-        if (row >= 0) {
-            const uint8_t* codes = r < kBM ? p.codes_a : p.codes_b;
-            const uint8_t* raw = r < kBM ? p.raw_a : p.raw_b;
-            loads.word[i] = __ldg(reinterpret_cast<const uint32_t*>(codes + row * (p.K / 2) + issue * 32) + c);
-            loads.byte[i] = __ldg(raw + ((row >> 7) * k_atoms + issue) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (c >> 1));
+        if (src.codes[i]) {
+            loads.word[i] = __ldg(src.codes[i] + issue * 8);           // 32 bytes of codes per row and issue
+            loads.byte[i] = __ldg(src.scale[i] + (int64_t)issue * 512); // one atom per 128 rows and issue
         }
     }
 }
 
-__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, const uint32_t* pair_lut,
-                                            int producer_thread) {
+__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, const ItemSources& src,
+                                            const uint32_t* pair_lut, int producer_thread) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
@@ -219,8 +218,9 @@ __device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoa
         const int r = item >> 3, c = item & 7;
         const int local = r < kBM ? r : r - kBM;
         unsigned char* tile = r < kBM ? stage : stage + kStageBytesA;
-        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) =
-            decode_word(loads.word[i], loads.byte[i], pair_lut);
+        // rows beyond the operand are zero (their results are never stored)
+        const uint4 value = src.codes[i] ? decode_word(loads.word[i], loads.byte[i], pair_lut) : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) = value;
     }
 }
 
@@ -302,32 +302,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const Tile tile = locate_tile(plan, t, p.M, p.N);
-            // operand rows of this thread's items, looked up once per tile
-            int item_row[kItems];
+            // sources of this thread's items, looked up once per tile
+            ItemSources src;
+            const int64_t k_atoms = p.K / 64;
 #pragma unroll
             for (int i = 0; i < kItems; ++i) {
-                const int r = (threadIdx.x + i * (kProducerWarps * 32)) >> 3;
+                const int item = threadIdx.x + i * (kProducerWarps * 32);
+                const int r = item >> 3, c = item & 7;
                 const bool is_a = r < kBM;
                 const int local = is_a ? tile.m0 + r : tile.n0 + (r - kBM);
                 const int count = is_a ? tile.rows : tile.cols;
-                item_row[i] = -1;
+                src.codes[i] = nullptr;
+                src.scale[i] = nullptr;
                 if (r < kBM + kBN && local < count) {
-                    if (is_a) item_row[i] = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
-                    else item_row[i] = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
+                    int64_t row;
+                    if (is_a) row = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
+                    else row = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
+                    src.codes[i] = reinterpret_cast<const uint32_t*>((is_a ? p.codes_a : p.codes_b) + row * (p.K / 2)) + c;
+                    src.scale[i] = (is_a ? p.raw_a : p.raw_b) + (row >> 7) * k_atoms * 512 + (row & 31) * 16 +
+                                   ((row >> 5) & 3) * 4 + (c >> 1);
                 }
             }
             StageLoads current, next;
-            load_stage(current, p, item_row, 0, threadIdx.x);
+            load_stage(current, src, 0);
             for (int j = 0; j < num_issues; ++j, ++g) {
                 const int s = g % kStages;
                 const uint32_t use = g / kStages;
-                if (j + 1 < num_issues) load_stage(next, p, item_row, j + 1, threadIdx.x);
+                if (j + 1 < num_issues) load_stage(next, src, j + 1);
                 if (use > 0) {
                     ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                 }
-                store_stage(smem + s * kStageBytes, current, bars->pair_lut, threadIdx.x);
+                store_stage(smem + s * kStageBytes, current, src, bars->pair_lut, threadIdx.x);
                 fence_generic_to_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->full[s]);
