@@ -15,8 +15,8 @@
 // cast.  The operands are not read as bf16 from memory: seven producer warps decode the packed
 // E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
 // 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
-// the record (every thread looks its rows up once per tile and issues all the global loads of
-// a stage before it decodes any, so their latencies overlap).  No workspace,
+// the record (every thread looks its rows up once per tile and keeps the global loads of three
+// issues in flight while it decodes an earlier one).  No workspace,
 // no separate decode pass.  Tiles are 128 x 128: a listed-row pass has few tiles, and the
 // narrower tile spreads them over twice as many SMs.  The issue counter runs on across tiles,
 // so the mbarrier phases never need re-initialising.
@@ -180,31 +180,33 @@ __device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale_byte,
 
 // One K=64 slab of the tile's A rows and B rows -> bf16 in the 128-byte-swizzled K-major
 // layout: row r of a tile occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk
-// position c ^ (r & 7).  An item is (row, 8-element chunk); every producer thread owns
-// kItems of them and issues all of their global loads before it decodes the first.
-constexpr int kStageItems = (kBM + kBN) * 8;
+// position c ^ (r & 7).  An item is (row, half of the issue): 16 bytes of codes (32 elements,
+// two 16-element blocks) and their two scale bytes in, four 16-byte chunks out.  Every producer
+// thread owns up to kItems of them and keeps the global loads of kPrefetch issues in flight,
+// so that DRAM latency is hidden behind the decoding of earlier issues.
+constexpr int kStageItems = (kBM + kBN) * 2;
 constexpr int kItems = (kStageItems + kProducerWarps * 32 - 1) / (kProducerWarps * 32);   // the last one may not exist
+constexpr int kPrefetch = 3;
 
 struct StageLoads {
-    uint32_t word[kItems];
-    uint32_t byte[kItems];
+    uint4 codes[kItems];
+    uint32_t scales[kItems];   // two bytes
 };
 
-// where a thread's items of the current tile live: the codes of (row, chunk) at issue 0 and the
-// row's raw scale byte of that chunk in atom 0; null for rows beyond the operand (and for the
-// last item of threads that have one item fewer)
+// where a thread's items of the current tile live: the codes of (row, half) at issue 0 and the
+// row's two raw scale bytes of that half in atom 0; null for rows beyond the operand (and for
+// the last item of threads that have one item fewer)
 struct ItemSources {
-    const uint32_t* codes[kItems];
-    const uint8_t* scale[kItems];
+    const uint4* codes[kItems];
+    const uint16_t* scale[kItems];
 };
 
-// issues the global loads of one stage (they complete while the previous stage is decoded)
 __device__ __forceinline__ void load_stage(StageLoads& loads, const ItemSources& src, int issue) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         if (src.codes[i]) {
-            loads.word[i] = __ldg(src.codes[i] + issue * 8);           // 32 bytes of codes per row and issue
-            loads.byte[i] = __ldg(src.scale[i] + (int64_t)issue * 512); // one atom per 128 rows and issue
+            loads.codes[i] = __ldg(src.codes[i] + issue * 2);             // 32 bytes of codes per row and issue
+            loads.scales[i] = __ldg(src.scale[i] + (int64_t)issue * 256);  // one 512-byte atom per 128 rows and issue
         }
     }
 }
@@ -215,12 +217,18 @@ __device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoa
     for (int i = 0; i < kItems; ++i) {
         const int item = producer_thread + i * (kProducerWarps * 32);
         if (item >= kStageItems) break;
-        const int r = item >> 3, c = item & 7;
+        const int r = item >> 1, half = item & 1;
         const int local = r < kBM ? r : r - kBM;
-        unsigned char* tile = r < kBM ? stage : stage + kStageBytesA;
-        // rows beyond the operand are zero (their results are never stored)
-        const uint4 value = src.codes[i] ? decode_word(loads.word[i], loads.byte[i], pair_lut) : make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile + local * 128 + ((c ^ (local & 7)) << 4)) = value;
+        unsigned char* row = (r < kBM ? stage : stage + kStageBytesA) + local * 128;
+        const uint32_t words[4] = {loads.codes[i].x, loads.codes[i].y, loads.codes[i].z, loads.codes[i].w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int c = half * 4 + w;   // 8-element chunk of the issue; chunks 2k, 2k+1 share block k's scale
+            // rows beyond the operand are zero (their results are never stored)
+            const uint4 value = src.codes[i] ? decode_word(words[w], (loads.scales[i] >> (8 * (w >> 1))) & 0xFFu, pair_lut)
+                                             : make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(row + ((c ^ (local & 7)) << 4)) = value;
+        }
     }
 }
 
@@ -308,37 +316,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
 #pragma unroll
             for (int i = 0; i < kItems; ++i) {
                 const int item = threadIdx.x + i * (kProducerWarps * 32);
-                const int r = item >> 3, c = item & 7;
+                const int r = item >> 1, half = item & 1;
                 const bool is_a = r < kBM;
                 const int local = is_a ? tile.m0 + r : tile.n0 + (r - kBM);
                 const int count = is_a ? tile.rows : tile.cols;
                 src.codes[i] = nullptr;
                 src.scale[i] = nullptr;
-                if (r < kBM + kBN && local < count) {
+                if (item < kStageItems && local < count) {
                     int64_t row;
                     if (is_a) row = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
                     else row = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
-                    src.codes[i] = reinterpret_cast<const uint32_t*>((is_a ? p.codes_a : p.codes_b) + row * (p.K / 2)) + c;
-                    src.scale[i] = (is_a ? p.raw_a : p.raw_b) + (row >> 7) * k_atoms * 512 + (row & 31) * 16 +
-                                   ((row >> 5) & 3) * 4 + (c >> 1);
+                    src.codes[i] = reinterpret_cast<const uint4*>((is_a ? p.codes_a : p.codes_b) + row * (p.K / 2)) + half;
+                    src.scale[i] = reinterpret_cast<const uint16_t*>(
+                        (is_a ? p.raw_a : p.raw_b) + (row >> 7) * k_atoms * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + half * 2);
                 }
             }
-            StageLoads current, next;
-            load_stage(current, src, 0);
-            for (int j = 0; j < num_issues; ++j, ++g) {
-                const int s = g % kStages;
-                const uint32_t use = g / kStages;
-                if (j + 1 < num_issues) load_stage(next, src, j + 1);
-                if (use > 0) {
-                    ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
-                    ok = __all_sync(0xFFFFFFFFu, ok);
-                    if (!ok) break;
+            StageLoads ring[kPrefetch + 1];
+#pragma unroll
+            for (int u = 0; u < kPrefetch; ++u)
+                if (u < num_issues) load_stage(ring[u], src, u);
+            for (int j0 = 0; j0 < num_issues && ok; j0 += kPrefetch + 1) {
+#pragma unroll
+                for (int u = 0; u < kPrefetch + 1; ++u) {
+                    const int j = j0 + u;
+                    if (j >= num_issues) break;
+                    if (j + kPrefetch < num_issues) load_stage(ring[(u + kPrefetch) % (kPrefetch + 1)], src, j + kPrefetch);
+                    const int s = g % kStages;
+                    const uint32_t use = g / kStages;
+                    if (use > 0) {
+                        ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
+                        if (!ok) break;
+                    }
+                    store_stage(smem + s * kStageBytes, ring[u], src, bars->pair_lut, threadIdx.x);
+                    fence_generic_to_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->full[s]);
+                    ++g;
                 }
-                store_stage(smem + s * kStageBytes, current, src, bars->pair_lut, threadIdx.x);
-                fence_generic_to_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->full[s]);
-                current = next;
             }
         }
     } else if (warp == kMmaWarp) {
@@ -468,7 +483,8 @@ extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_
     if (ldo < N) return UE5M3_ERR_INVALID_ARGUMENT;
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
     if (((M + 127) / 128) * ((N + 255) / 256) > 0x3FFFFFFF) return UE5M3_ERR_TOO_LARGE;
-    if (((uintptr_t)a_codes % 4) || ((uintptr_t)b_codes % 4)) return UE5M3_ERR_ALIGNMENT;
+    if (((uintptr_t)a_codes % 16) || ((uintptr_t)b_codes % 16) || ((uintptr_t)a_sf_raw % 4) || ((uintptr_t)b_sf_raw % 4))
+        return UE5M3_ERR_ALIGNMENT;
 
     fb::Params p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
