@@ -608,3 +608,39 @@ def test_hadamard_transformed_operand_against_the_oracle(b200, k, rows, sr, dtyp
     sf = b200.pack_scales(torch.from_numpy(ref["scales"]).cuda(), rows=rows, k=k, block_size=16, two_dimensional=False,
                           shift=shift)
     assert torch.equal(op.scale_factors, sf)
+
+
+def test_launches_after_a_recorded_failure_mark_their_output(b200):
+    """A GEMM launch that finds a failure in the status word does no work; it must not leave the
+    output looking like a result.  The failure is written by the host here (nothing waits, nothing
+    faults): every element of both kernels' outputs is NaN, including ragged edges, and the host
+    check raises and clears the word."""
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(300, 256, generator=g).to(torch.bfloat16).cuda()
+    bt = torch.randn(200, 256, generator=g).to(torch.bfloat16).cuda()
+    amax = torch.ones(1, device=dev) * 8.0
+    op_a = b200.quantize_fp4_operand(a, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
+                                     scale_target=448.0)
+    op_b = b200.quantize_fp4_operand(bt, block_size=16, blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax,
+                                     scale_target=448.0)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    words = b200.gemm_status(dev)
+    words.copy_(torch.tensor([1, 99, 7, 3], dtype=torch.int32))
+    try:
+        for out_dtype in (torch.float32, torch.bfloat16):
+            got_fp4 = b200.gemm_fp4_operands(op_a, op_b, snap=True, out_dtype=out_dtype)
+            got_rz = b200.gemm_issue_rz(a, bt, snap=True, out_dtype=out_dtype)
+            torch.cuda.synchronize()
+            assert got_fp4.shape == got_rz.shape == (300, 200)
+            assert bool(torch.isnan(got_fp4).all()) and bool(torch.isnan(got_rz).all())
+        with pytest.raises(RuntimeError, match="site 99"):
+            b200.check_gemm_status(dev)
+    finally:
+        words.zero_()
+    healthy = b200.gemm_fp4_operands(op_a, op_b, snap=True)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    assert bool(torch.isfinite(healthy).all())

@@ -12,17 +12,19 @@
 //   A x B over the whole output    -> when a list overflowed its capacity,
 // and per tile do what gemm_sm100.cu does: four K=16 BF16 MMAs into a fresh TMEM accumulator
 // per K=64 issue, round-toward-zero adds across issues in registers, then snap, alpha, bias,
-// cast.  The operands are not read as bf16 from memory: seven producer warps decode the packed
+// cast.  The operands are not read as bf16 from memory: twelve producer warps decode the packed
 // E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
 // 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
-// the record (every thread looks its rows up once per tile and keeps the global loads of three
-// issues in flight while it decodes an earlier one).  No workspace,
-// no separate decode pass.  Tiles are 128 x 128: a listed-row pass has few tiles, and the
-// narrower tile spreads them over twice as many SMs.  The issue counter runs on across tiles,
-// so the mbarrier phases never need re-initialising.
+// the record (every thread looks its rows up once per tile and has the next issue's global loads
+// in flight while it decodes the current one).  No workspace, no separate decode pass.  Tiles
+// are 128 x 64: a listed-row pass has one or two row tiles, and the narrow tile spreads them over
+// more SMs while each CTA decodes fewer rows of the full operand per issue.  The issue counter
+// runs on across tiles, so the mbarrier phases never need re-initialising.
 //
-// Warps: 0..6 producers, 7 MMA issuer and TMEM owner, 8..15 epilogue (TMEM lane quadrant =
-// warp % 4, column half = (warp - 8) / 4).  Every wait is clock-bounded.
+// Warps: 0..11 producers, 12 MMA issuer and TMEM owner, 13..20 epilogue (TMEM lane quadrant =
+// warp % 4, column half = (warp - 13) / 4).  Of the producers and of the epilogue warps only
+// one warp each polls its mbarrier; the others sleep on a hardware barrier and take the outcome
+// from shared memory (group_wait).  Every mbarrier wait is clock-bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -41,15 +43,15 @@ using namespace ptx;
 namespace fb {
 
 constexpr int kBM = 128;
-constexpr int kBN = 128;
+constexpr int kBN = 64;    // narrow: a listed-row pass has few row tiles, so the columns must spread it over the SMs
 constexpr int kBK = 64;
-constexpr int kStages = 6;
-constexpr int kProducerWarps = 7;   // 16 warps in all: register files are handed out per four warps
+constexpr int kStages = 8;
+constexpr int kProducerWarps = 12;  // one 16-byte item per thread and issue
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kEpilogueWarp0 = kMmaWarp + 1;
-constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueWarps = 8;   // 32 lanes x 32 columns each
 constexpr int kThreads = 32 * (kEpilogueWarp0 + kEpilogueWarps);
-constexpr uint32_t kTmemCols = 256;   // two 128-column accumulators
+constexpr uint32_t kTmemCols = 2 * kBN;   // two accumulators
 constexpr uint32_t kStageBytesA = kBM * kBK * 2;
 constexpr uint32_t kStageBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
@@ -98,7 +100,8 @@ struct __align__(8) Barriers {
     unsigned long long tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
-    uint32_t pair_lut[256];   // packed byte (two E2M1 codes) -> their two values as a bf16 pair
+    int producers_go[2];   // outcome of the producers' / the epilogue's current wait (group_wait)
+    int epilogue_go[2];
 };
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -162,17 +165,70 @@ __device__ __forceinline__ Tile locate_tile(const Plan& plan, int t, int M, int 
     return tile;
 }
 
-// eight codes (one 32-bit word) x one scale -> eight bf16 values: per byte one table lookup
-// (the two payload values as a bf16 pair) and one packed bf16 multiply by the scale, which is
-// exact (a 2-bit by a 4-bit significand)
-__device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale_byte, const uint32_t* pair_lut) {
-    const __nv_bfloat16 scale = __float2bfloat16_rn(ue5m3_decode(scale_byte));   // 4 significant bits: exact
-    const __nv_bfloat162 scale2 = __halves2bfloat162(scale, scale);
+// prmt.b32 as the hardware defines it: bit 3 of a selector nibble replicates the selected byte's
+// top bit over the result byte (the __byte_perm intrinsic promises the low three bits only).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+
+// Barrier `id` of the CTA over `threads` threads: waiting warps take no issue slots, unlike
+// warps polling an mbarrier.  Every thread of the group must arrive.
+__device__ __forceinline__ void group_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// One warp of a group waits on the mbarrier, the others sleep on a hardware barrier and learn
+// the outcome from shared memory - so that they all leave their loop in the same iteration and
+// nobody is left behind at the hardware barrier, which has no time limit of its own.  `word` is
+// double-buffered by the caller (iteration parity).
+__device__ __forceinline__ bool group_wait(bool poller, int id, int threads, volatile int* word, unsigned long long* bar,
+                                           uint32_t parity, int* abort_flag, int* status, int where, int iter) {
+    __syncwarp();   // the hardware barrier wants the whole warp at once
+    if (poller) {
+        bool ok = mbar_wait(bar, parity, abort_flag, status, where, iter);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if ((threadIdx.x & 31) == 0) *word = ok ? 1 : 0;
+    }
+    group_sync(id, threads);
+    return *word != 0;
+}
+
+// A UE5M3 scale byte as a bf16 pair (both halves the same).  A normal byte E<<3|M is the bf16
+// (E + 112) << 7 | M << 4; the seven subnormal bytes take the slow way; byte 0 (an all-zero
+// block, or padding) gives 0.
+__device__ __forceinline__ uint32_t scale_pair(uint32_t scale_byte) {
+    uint32_t bits = (scale_byte << 4) + 0x3800u;
+    if (scale_byte < 8u) bits = __bfloat16_as_ushort(__float2bfloat16_rn(ue5m3_decode(scale_byte)));
+    return __byte_perm(bits, bits, 0x1010);
+}
+
+// Eight codes (one 32-bit word) x one scale -> eight bf16 values, in registers only.  A byte
+// permute is a four-way lookup in an eight-byte table, which is exactly an E2M1 magnitude (3
+// bits) -> one byte of its bf16 encoding: two permutes give the high bytes of eight codes, two
+// the low bytes.  The sign bit of a code is bit 3 of its nibble, which a permute's selector reads
+// as "replicate the selected byte's top bit": over a table of 0x80 bytes that yields 0xFF for a
+// negative code and 0x80 otherwise, and bit 6 of that byte, moved up by one, is the bf16 sign.
+// The packed multiply by the scale is exact (a 2-bit by a 4-bit significand).
+__device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale2_bits) {
+    constexpr uint32_t kHighA = 0x3F3F3F00u, kHighB = 0x40404040u;   // 0 .5 1 1.5 | 2 3 4 6
+    constexpr uint32_t kLowA = 0xC0800000u, kLowB = 0xC0804000u;
+    const uint32_t mag = word & 0x77777777u;
+    const uint32_t word_hi = word >> 16, mag_hi = mag >> 16;
+    uint32_t high0 = prmt(kHighA, kHighB, mag), low0 = prmt(kLowA, kLowB, mag);
+    uint32_t high1 = prmt(kHighA, kHighB, mag_hi), low1 = prmt(kLowA, kLowB, mag_hi);
+    const uint32_t neg0 = prmt(0x80808080u, 0x80808080u, word & 0xFFFFu);
+    const uint32_t neg1 = prmt(0x80808080u, 0x80808080u, word_hi);
+    high0 |= (neg0 << 1) & 0x80808080u;
+    high1 |= (neg1 << 1) & 0x80808080u;
+    const uint32_t pairs[4] = {__byte_perm(low0, high0, 0x5140), __byte_perm(low0, high0, 0x7362),
+                               __byte_perm(low1, high1, 0x5140), __byte_perm(low1, high1, 0x7362)};
+    const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&scale2_bits);
     uint32_t out[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t bits = pair_lut[(word >> (8 * i)) & 0xFFu];
-        const __nv_bfloat162 product = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits), scale2);
+        const __nv_bfloat162 product = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pairs[i]), scale2);
         out[i] = *reinterpret_cast<const uint32_t*>(&product);
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
@@ -181,25 +237,37 @@ __device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale_byte,
 // One K=64 slab of the tile's A rows and B rows -> bf16 in the 128-byte-swizzled K-major
 // layout: row r of a tile occupies 128 bytes at r * 128, its 16-byte chunk c sits at chunk
 // position c ^ (r & 7).  An item is (row, half of the issue): 16 bytes of codes (32 elements,
-// two 16-element blocks) and their two scale bytes in, four 16-byte chunks out.  Every producer
-// thread owns up to kItems of them and keeps the global loads of kPrefetch issues in flight,
-// so that DRAM latency is hidden behind the decoding of earlier issues.
+// two 16-element blocks) and their two scale bytes in, four 16-byte chunks out.  The 512 items
+// of a stage go one to a producer thread; the 32 left over are second items of warp 0, taken
+// from the operand that a row or column pass has few rows of (see item_row).  Every thread has
+// the next issue's global loads in flight while it decodes the current one.
 constexpr int kStageItems = (kBM + kBN) * 2;
 constexpr int kItems = (kStageItems + kProducerWarps * 32 - 1) / (kProducerWarps * 32);   // the last one may not exist
-constexpr int kPrefetch = 3;
+static_assert(kItems * kProducerWarps * 32 >= kStageItems && kEpilogueWarps * 32 * 32 == kBM * kBN, "warp roles cover a stage and a tile");
+
+constexpr int kPrefetch = 1;
 
 struct StageLoads {
     uint4 codes[kItems];
     uint32_t scales[kItems];   // two bytes
 };
 
-// where a thread's items of the current tile live: the codes of (row, half) at issue 0 and the
-// row's two raw scale bytes of that half in atom 0; null for rows beyond the operand (and for
-// the last item of threads that have one item fewer)
+// where a thread's items of the current tile live: the codes of (row, half) at issue 0, the
+// row's two raw scale bytes of that half in atom 0, and the row's 128 bytes in a stage.  A null
+// pointer marks a row beyond the operand: zeros are stored for it.  stage_offset < 0: no item.
 struct ItemSources {
     const uint4* codes[kItems];
     const uint16_t* scale[kItems];
+    int stage_offset[kItems];
 };
+
+// Row of the stage (0..kBM-1 operand A, kBM.. operand B) that an item belongs to.  In a row pass
+// operand B comes first, so that the leftover items are rows of A's tile, of which such a pass
+// has few; in the other passes operand A comes first.
+__device__ __forceinline__ int item_row(int item, int job) {
+    const int r = item >> 1;
+    return job == 0 ? (r < kBN ? r + kBM : r - kBN) : r;
+}
 
 __device__ __forceinline__ void load_stage(StageLoads& loads, const ItemSources& src, int issue) {
 #pragma unroll
@@ -211,23 +279,25 @@ __device__ __forceinline__ void load_stage(StageLoads& loads, const ItemSources&
     }
 }
 
-__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, const ItemSources& src,
-                                            const uint32_t* pair_lut, int producer_thread) {
+__device__ __forceinline__ void store_stage(unsigned char* stage, const StageLoads& loads, const ItemSources& src) {
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
-        const int item = producer_thread + i * (kProducerWarps * 32);
-        if (item >= kStageItems) break;
-        const int r = item >> 1, half = item & 1;
-        const int local = r < kBM ? r : r - kBM;
-        unsigned char* row = (r < kBM ? stage : stage + kStageBytesA) + local * 128;
+        if (src.stage_offset[i] < 0) break;
+        unsigned char* row = stage + (src.stage_offset[i] & ~1);
+        const int half = src.stage_offset[i] & 1;
+        const int swizzle = (src.stage_offset[i] >> 7) & 7;   // both operands' regions start on 1024 bytes
         const uint32_t words[4] = {loads.codes[i].x, loads.codes[i].y, loads.codes[i].z, loads.codes[i].w};
+        uint32_t scale2[2] = {0u, 0u};
+        if (src.codes[i]) {
+            scale2[0] = scale_pair(loads.scales[i] & 0xFFu);
+            scale2[1] = scale_pair((loads.scales[i] >> 8) & 0xFFu);
+        }
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const int c = half * 4 + w;   // 8-element chunk of the issue; chunks 2k, 2k+1 share block k's scale
             // rows beyond the operand are zero (their results are never stored)
-            const uint4 value = src.codes[i] ? decode_word(words[w], (loads.scales[i] >> (8 * (w >> 1))) & 0xFFu, pair_lut)
-                                             : make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(row + ((c ^ (local & 7)) << 4)) = value;
+            const uint4 value = src.codes[i] ? decode_word(words[w], scale2[w >> 1]) : make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(row + ((c ^ swizzle) << 4)) = value;
         }
     }
 }
@@ -239,16 +309,16 @@ __device__ __forceinline__ float to_out<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// one thread's 128 finished values of one output row
+// one thread's finished values of one output row
 template <typename OutT>
-__device__ __forceinline__ void store_row(const Params& p, const Tile& tile, const float (&c)[kBN / 2],
+__device__ __forceinline__ void store_row(const Params& p, const Tile& tile, const float (&c)[32],
                                           long long out_row, int col0) {
     OutT* out = static_cast<OutT*>(p.out) + out_row * p.ldo;
     const int* col_map = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
     constexpr int kVec = 16 / (int)sizeof(OutT);
     const bool vec = !col_map && (p.ldo % kVec) == 0 && ((uintptr_t)p.out % 16) == 0;
 #pragma unroll
-    for (int i = 0; i < kBN / 2; i += kVec) {
+    for (int i = 0; i < 32; i += kVec) {
         if (vec && col0 + i + kVec <= tile.cols) {
             OutT tmp[kVec];
 #pragma unroll
@@ -292,10 +362,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
         mbar_fence_init();
     }
     if (warp == kMmaWarp) tmem_alloc(&bars->tmem_base, kTmemCols);
-    if (threadIdx.x < 256) {
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(e2m1_value(threadIdx.x & 0xFu), e2m1_value(threadIdx.x >> 4));
-        bars->pair_lut[threadIdx.x] = *reinterpret_cast<const uint32_t*>(&pair);
-    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -316,16 +382,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
 #pragma unroll
             for (int i = 0; i < kItems; ++i) {
                 const int item = threadIdx.x + i * (kProducerWarps * 32);
-                const int r = item >> 1, half = item & 1;
+                const int r = item_row(item, tile.job), half = item & 1;
                 const bool is_a = r < kBM;
-                const int local = is_a ? tile.m0 + r : tile.n0 + (r - kBM);
+                const int local = is_a ? r : r - kBM;
+                const int index = (is_a ? tile.m0 : tile.n0) + local;
                 const int count = is_a ? tile.rows : tile.cols;
                 src.codes[i] = nullptr;
                 src.scale[i] = nullptr;
-                if (item < kStageItems && local < count) {
+                src.stage_offset[i] = item < kStageItems ? ((is_a ? 0 : (int)kStageBytesA) + local * 128) | half : -1;
+                if (item < kStageItems && index < count) {
                     int64_t row;
-                    if (is_a) row = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + local) : local;
-                    else row = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + local) : local;
+                    if (is_a) row = tile.job == 0 ? __ldg(p.rec_a + kRecHeader + index) : index;
+                    else row = tile.job == 1 ? __ldg(p.rec_b + kRecHeader + index) : index;
                     src.codes[i] = reinterpret_cast<const uint4*>((is_a ? p.codes_a : p.codes_b) + row * (p.K / 2)) + half;
                     src.scale[i] = reinterpret_cast<const uint16_t*>(
                         (is_a ? p.raw_a : p.raw_b) + (row >> 7) * k_atoms * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + half * 2);
@@ -344,11 +412,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
                     const int s = g % kStages;
                     const uint32_t use = g / kStages;
                     if (use > 0) {
-                        ok = mbar_wait(&bars->empty[s], (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
-                        ok = __all_sync(0xFFFFFFFFu, ok);
+                        ok = group_wait(warp == 0, 1, kProducerWarps * 32, &bars->producers_go[g & 1], &bars->empty[s],
+                                        (use - 1) & 1, &bars->abort_flag, p.status, 11, g);
                         if (!ok) break;
                     }
-                    store_stage(smem + s * kStageBytes, ring[u], src, bars->pair_lut, threadIdx.x);
+                    store_stage(smem + s * kStageBytes, ring[u], src);
                     fence_generic_to_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->full[s]);
@@ -390,36 +458,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
         }
     } else {
         // ---------------- epilogue ----------------
+        constexpr int kCols = 32;          // columns per epilogue warp
         const int q = warp & 3;
         const int h = (warp - kEpilogueWarp0) >> 2;
         const float alpha = alpha_value(p.alpha);
-        const bool scale_by_alpha = alpha_enabled(p.alpha);
         int g = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const Tile tile = locate_tile(plan, t, p.M, p.N);
-            float c[kBN / 2];
+            float c[kCols];
 #pragma unroll
-            for (int i = 0; i < kBN / 2; ++i) c[i] = 0.0f;
+            for (int i = 0; i < kCols; ++i) c[i] = 0.0f;
             for (int j = 0; j < num_issues; ++j, ++g) {
                 const int b = g & 1;
-                ok = mbar_wait(&bars->tmem_full[b], (g >> 1) & 1, &bars->abort_flag, p.status, 14, g);
-                ok = __all_sync(0xFFFFFFFFu, ok);
+                ok = group_wait(warp == kEpilogueWarp0, 2, kEpilogueWarps * 32, &bars->epilogue_go[b], &bars->tmem_full[b],
+                                (g >> 1) & 1, &bars->abort_flag, p.status, 14, g);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * (kBN / 2));
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * kCols);
+                uint32_t v[32];
+                tmem_load_32_async(taddr, v);
+                tmem_wait_ld();
 #pragma unroll
-                for (int half = 0; half < kBN / 2 / 64; ++half) {
-                    uint32_t v0[32], v1[32];
-                    tmem_load_32_async(taddr + half * 64, v0);
-                    tmem_load_32_async(taddr + half * 64 + 32, v1);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        fadd2_rz(c[half * 64 + i], c[half * 64 + i + 1], v0[i], v0[i + 1]);
-                        fadd2_rz(c[half * 64 + 32 + i], c[half * 64 + 33 + i], v1[i], v1[i + 1]);
-                    }
-                }
+                for (int i = 0; i < 32; i += 2) fadd2_rz(c[i], c[i + 1], v[i], v[i + 1]);
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
@@ -428,18 +489,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fallback_kernel(const Params
             const int local_row = tile.m0 + q * 32 + lane;
             if (local_row >= tile.rows) continue;
             const long long out_row = tile.job == 0 ? (long long)__ldg(p.rec_a + kRecHeader + local_row) : local_row;
-            const int col0 = tile.n0 + h * (kBN / 2);
+            const int col0 = tile.n0 + h * kCols;
             const int* col_map = tile.job == 1 ? p.rec_b + kRecHeader : nullptr;
 #pragma unroll
-            for (int i = 0; i < kBN / 2; ++i) {
+            for (int i = 0; i < kCols; ++i) {
                 float v = c[i];
                 if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
-                if (scale_by_alpha) v = __fmul_rn(v, alpha);
-                c[i] = v;
+                c[i] = __fmul_rn(v, alpha);   // alpha is 1 when the caller gave none: an exact no-op
             }
             if (p.bias) {
 #pragma unroll
-                for (int i = 0; i < kBN / 2; ++i) {
+                for (int i = 0; i < kCols; ++i) {
                     const int col = col0 + i;
                     if (col < tile.cols) {
                         const int out_col = col_map ? __ldg(col_map + col) : col;
@@ -482,7 +542,7 @@ extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_
     if (bias && bias_dtype != UE5M3_DTYPE_BF16 && bias_dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
     if (ldo < N) return UE5M3_ERR_INVALID_ARGUMENT;
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
-    if (((M + 127) / 128) * ((N + 255) / 256) > 0x3FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    if (((M + fb::kBM - 1) / fb::kBM) * ((N + fb::kBN - 1) / fb::kBN) > 0x3FFFFFFF) return UE5M3_ERR_TOO_LARGE;
     if (((uintptr_t)a_codes % 16) || ((uintptr_t)b_codes % 16) || ((uintptr_t)a_sf_raw % 4) || ((uintptr_t)b_sf_raw % 4))
         return UE5M3_ERR_ALIGNMENT;
 

@@ -28,6 +28,7 @@
 
 #include "abi_common.cuh"
 #include "alpha_spec.cuh"
+#include "dead_fill.cuh"
 #include "tcgen05_ptx.cuh"
 #include "window_record.cuh"
 
@@ -344,7 +345,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool dead = *((volatile int*)&bars->abort_flag) != 0;
 
     if (dead) {
-        // fall through to the common exit
+        // no work after a recorded failure: mark this CTA's tiles and fall through to the common exit
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int tile_m, tile_n;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+            fill_tile_nan(p.out, p.out_dtype == UE5M3_DTYPE_BF16, p.ldo, tile_m * kFM, tile_n * kFN, kFM, kFN, p.M, p.N);
+        }
     } else if (warp == 0) {
         // ---------------- producer: operands by TMA, scale atoms by bulk copy ----------------
         {
@@ -621,7 +627,13 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const bool dead = *((volatile int*)&bars->abort_flag) != 0;
 
     if (dead) {
-        // fall through to the common exit
+        // no work after a recorded failure: mark this CTA's half of the pair's tiles, then the common exit
+        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+            int tile_m, tile_n;
+            pair_tile_coords(tile, p.tiles_m, p.tiles_n, tile_m, tile_n);
+            fill_tile_nan(p.out, p.out_dtype == UE5M3_DTYPE_BF16, p.ldo, tile_m * kPM + (int)rank * 128, tile_n * kFN, 128,
+                          kFN, p.M, p.N);
+        }
     } else if (warp == 0) {
         // ---------------- producer (both CTAs): own A rows, own B half, own scale atoms ----------------
         {

@@ -28,6 +28,7 @@
 
 #include "abi_common.cuh"
 #include "alpha_spec.cuh"
+#include "dead_fill.cuh"
 
 namespace ue5m3 {
 
@@ -280,7 +281,8 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool dead = *((volatile int*)&bars->abort_flag) != 0;
 
     if (dead) {
-        // fall through to the common exit
+        // no work after a recorded failure: mark this CTA's tile and fall through to the common exit
+        fill_tile_nan(p.out, p.out_dtype == UE5M3_DTYPE_BF16, p.ldo, m0, n0, kBM, kBN, p.M, p.N);
     } else if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
