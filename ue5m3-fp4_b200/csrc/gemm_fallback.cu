@@ -12,17 +12,17 @@
 //   A x B over the whole output    -> when a list overflowed its capacity,
 // and per tile do what gemm_sm100.cu does: four K=16 BF16 MMAs into a fresh TMEM accumulator
 // per K=64 issue, round-toward-zero adds across issues in registers, then snap, alpha, bias,
-// cast.  The operands are not read as bf16 from memory: twelve producer warps decode the packed
+// cast.  The operands are not read as bf16 from memory: ten producer warps decode the packed
 // E2M1 codes and the RAW UE5M3 scale atoms (p * s is exact in bf16) straight into the
 // 128-byte-swizzled K-major shared-memory tiles the MMA reads, gathering listed rows through
 // the record (every thread looks its rows up once per tile and has the next issue's global loads
 // in flight while it decodes the current one).  No workspace, no separate decode pass.  Tiles
-// are 128 x 64: a listed-row pass has one or two row tiles, and the narrow tile spreads them over
+// are 128 x 32: a listed-row pass has one or two row tiles, and the narrow tile spreads them over
 // more SMs while each CTA decodes fewer rows of the full operand per issue.  The issue counter
 // runs on across tiles, so the mbarrier phases never need re-initialising.
 //
-// Warps: 0..11 producers, 12 MMA issuer and TMEM owner, 13..20 epilogue (TMEM lane quadrant =
-// warp % 4, column half = (warp - 13) / 4).  Of the producers and of the epilogue warps only
+// Warps: 0..9 producers, 10 MMA issuer and TMEM owner, 11..14 epilogue (TMEM lane quadrant =
+// warp % 4).  Of the producers and of the epilogue warps only
 // one warp each polls its mbarrier; the others sleep on a hardware barrier and take the outcome
 // from shared memory (group_wait).  Every mbarrier wait is clock-bounded.
 #include <cuda.h>
@@ -43,13 +43,13 @@ using namespace ptx;
 namespace fb {
 
 constexpr int kBM = 128;
-constexpr int kBN = 64;    // narrow: a listed-row pass has few row tiles, so the columns must spread it over the SMs
+constexpr int kBN = 32;    // narrow: a listed-row pass has few row tiles, so the columns must spread it over the SMs
 constexpr int kBK = 64;
-constexpr int kStages = 8;
-constexpr int kProducerWarps = 12;  // one 16-byte item per thread and issue
+constexpr int kStages = 10;
+constexpr int kProducerWarps = 10;  // one 16-byte item per thread and issue
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kEpilogueWarp0 = kMmaWarp + 1;
-constexpr int kEpilogueWarps = 8;   // 32 lanes x 32 columns each
+constexpr int kEpilogueWarps = 4;   // 32 lanes x 32 columns each
 constexpr int kThreads = 32 * (kEpilogueWarp0 + kEpilogueWarps);
 constexpr uint32_t kTmemCols = 2 * kBN;   // two accumulators
 constexpr uint32_t kStageBytesA = kBM * kBK * 2;
