@@ -541,7 +541,7 @@ def _round_trip_c1(torch, ops, device, steps: int, peaks: dict) -> dict:
             "frac_of_hbm_peak": algorithmic / seconds / 1e9 / peaks["hbm_gbs"], "launches_timed": 2 * steps}
 
 
-def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: int) -> dict:
+def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: int, compare_bf16: bool = True) -> dict:
     """One data-parallel training step of the Nemotron-H-8B-shaped stack (112 FP4 linears at their
     real shapes, stand-in mixers, FP32 vocabulary head): uniform random token ids, sequence 8192,
     micro-batch 1 per GPU, forward + backward + optimizer step, torch DDP with bf16 gradient
@@ -636,11 +636,58 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         }
         del optimizer, wrapped, model
         torch.cuda.empty_cache()
+        if world == 1 and compare_bf16:
+            # the same stack and step with its 112 linears left as bf16 nn.Linear (cuBLAS): what the
+            # FP4 path costs or saves at the level of a training step
+            result["ms_hold_step_bf16_linears"] = _c5_bf16_step(torch, device, seq)
         return result
     except Exception as error:  # noqa: BLE001 - reported, the headline does not depend on it
         import traceback
 
         return {"error": f"{type(error).__name__}: {error}"[:400], "trace": traceback.format_exc()[-600:]}
+
+
+def _c5_bf16_step(torch, device, seq: int) -> float | str:
+    """ms per step of the unconverted Nemotron-H-shaped stack (bf16 linears), same batch, optimizer and head."""
+
+    import torch.nn.functional as F
+
+    from ue5m3_fp4.integrations.torchtitan.shaped_stack import NemotronHShapedStack
+
+    try:
+        torch.manual_seed(0)
+        model = NemotronHShapedStack(device=device, dtype=torch.bfloat16)
+        model.lm_head.to(torch.float32)   # FP32 head on FP32 inputs, as the converted stack has it
+        model.lm_head.register_forward_pre_hook(lambda module, inputs: (inputs[0].float(),))
+        previous_tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        optimizer = torch.optim.AdamW(model.parameters(), lr=0.0, fused=True)
+        g = torch.Generator(device=device).manual_seed(100)
+
+        def step() -> None:
+            ids = torch.randint(0, model.config.vocab_size, (1, seq), device=device, generator=g)
+            labels = torch.roll(ids, -1, dims=1).reshape(-1)
+            logits = model(ids)
+            F.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels).backward()
+            optimizer.step()
+            optimizer.zero_grad(set_to_none=True)
+
+        step()
+        step()
+        torch.cuda.synchronize(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(3):
+            step()
+        stop.record()
+        torch.cuda.synchronize(device)
+        torch.backends.cuda.matmul.allow_tf32 = previous_tf32
+        elapsed = start.elapsed_time(stop) / 3
+        del optimizer, model
+        torch.cuda.empty_cache()
+        return elapsed
+    except Exception as error:  # noqa: BLE001 - a comparison figure only
+        return f"{type(error).__name__}: {error}"[:300]
 
 
 def run_ours(args) -> None:
@@ -808,6 +855,11 @@ def run_case(args) -> None:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(0)
+    if args.case == "c5-step":
+        # the Nemotron-H-shaped training step alone (launch-list captures of one step: 336 products)
+        result = _c5_training_step(torch, None, device, 0, 1, 0, compare_bf16=False)
+        print(json.dumps({k: result.get(k) for k in ("ms_hold_step", "ms_refresh_step", "error")}))
+        return
     if args.case == "gemm-small":
         m, n = 4096, 8192  # operands + output 160 MB: larger than L2, 2048 tiles
         a = torch.randn(m, K, generator=g).to(torch.bfloat16).to(device)
@@ -894,7 +946,7 @@ def run_case(args) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize", "linear-step", "fallback-small"],
+    parser.add_argument("--case", default=None, choices=["gemm-small", "gemm-fp4-small", "quantize", "linear-step", "fallback-small", "c5-step"],
                         help="run one small kernel case for a profiler capture instead of the benchmark")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
