@@ -312,8 +312,8 @@ int ue5m3_gemm_fp4(const uint8_t *a_codes, const uint8_t *a_sf, const uint8_t *b
  * when a list overflowed) with the result of the issue-RZ kernel of ue5m3_gemm_issue_rz_bf16
  * on the exact encoded operands, which its producer warps decode from the codes and the raw
  * UE5M3 scale atoms (sf_raw of the quantizers) straight into shared memory.  The records are
- * read on the device: no host synchronisation, no workspace, and with empty records the one
- * launch returns at once.  This is what makes the FP4 path produce the reference model's
+ * read on the device: no host synchronisation, no workspace, and with empty records the two
+ * launches (one per tile width: listed rows, listed columns) return at once.  This is what makes the FP4 path produce the reference model's
  * result for every tensor the reference accepts (its UE5M3 scales have no window,
  * formats.py:125-134, backends/triton/quantization.py:116-127).
  */
