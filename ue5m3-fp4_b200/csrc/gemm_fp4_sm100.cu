@@ -7,19 +7,24 @@
 // scale type by a per-tensor power of two (ue5m3_pack_scales_ue4m3 below): both formats
 // carry three fraction bits, so inside a 15-binade window the re-biased scale is the same
 // number divided by 2^shift, and the epilogue multiplies the result by 2^(shift_a+shift_b),
-// which is exact.  A scale outside the window raises the caller's window flag; the caller
-// then uses the BF16-issue kernel (gemm_sm100.cu), which has no such restriction.
+// which is exact.  A row whose scales do not fit the window at the tensor's shift is flagged in
+// the operand's window record by the quantizer; ue5m3_place_row_windows (window_place.cu) gives
+// such a row a shift of its own where its scales span at most 15 binades - the epilogue here then
+// also multiplies by 2^(row shift + column shift) - and lists the rows that still do not fit,
+// whose output rows / columns ue5m3_gemm_fp4_fallback (gemm_fallback.cu) overwrites afterwards.
 //
 // One tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X instruction multiplies a
-// 128 x 256 x 64 slab, i.e. exactly one K=64 issue of the reference model (four 16-blocks
-// per operand row), and accumulates it into the FP32 tile in TMEM; the K loop is a plain
-// chain of such instructions.
+// 128 x 256 x 64 slab (256 x 256 x 64 for a CTA pair), i.e. exactly one K=64 issue of the
+// reference model (four 16-blocks per operand row), and accumulates it into the FP32 tile in
+// TMEM; the K loop is a plain chain of such instructions.
 //
-// Tiling: persistent CTAs (one per SM) walk 128 x 256 output tiles.  A stage holds K = 256
-// (128 bytes per row, one 128-byte swizzle atom): A 16 KiB + B 32 KiB + scale atoms 2 + 4 KiB;
-// four stages.  Warp 0 = TMA/bulk-copy producer, warp 1 = scale copies (shared -> TMEM) and
-// MMA issue, warps 2..9 = epilogue (lane quadrant = warp % 4, column half = (warp - 2) / 4).
-// All waits are clock-bounded.
+// Two kernels.  gemm_fp4_kernel (M <= 128): persistent CTAs (one per SM) walk 128 x 256 output
+// tiles; a stage holds K = 256 (128 bytes per row, one 128-byte swizzle atom): A 16 KiB +
+// B 32 KiB + scale atoms 2 + 4 KiB; four stages.  Warp 0 = TMA producer, warp 1 = MMA issue,
+// warps 2..9 = epilogue (lane quadrant = warp % 4, column half = (warp - 2) / 4), warps 10..11 =
+// scale copies shared -> TMEM.  gemm_fp4_pair_kernel (the default otherwise): the same roles in a
+// cluster of two CTAs, described above its definition.  All waits are clock-bounded; a launch
+// that finds a failure recorded in its status word fills its output with NaN instead of working.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
@@ -938,7 +943,8 @@ static int make_sf_map(CUtensorMap* map, const void* base, int64_t atoms) {
 
 // The CTA-pair kernel is used when there is more than one 128-row tile; UE5M3_FP4_CTA_PAIR=0/1
 // in the environment (read at every call) forces the single-CTA / the pair kernel.  The two are
-// bit-equal; on the benchmark shape the pair kernel takes 0.337 ms against 0.353 ms.
+// bit-equal; the pair kernel is the faster one wherever both apply (about 5 % on the
+// 8192 x 21504 x 4096 product).
 static bool use_cta_pair(int64_t M) {
     const char* e = getenv("UE5M3_FP4_CTA_PAIR");
     if (e && (e[0] == '0' || e[0] == '1')) return e[0] == '1';
