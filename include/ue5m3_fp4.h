@@ -325,6 +325,27 @@ int ue5m3_gemm_fp4_fallback(const uint8_t *a_codes, const uint8_t *a_sf_raw, con
                             int out_dtype, int64_t ldo, int *status_dev, void *stream);
 
 /*
+ * ue5m3_gemm_fp4_fallback with a caller-provided device workspace of at least
+ * ue5m3_fallback_workspace_bytes(M, N, K) bytes (16-byte aligned; contents need not be
+ * preserved between calls): every needed operand row is decoded once into the workspace
+ * (listed rows gathered; the other operand in full, and only when something is listed) and
+ * the issue-RZ kernel of ue5m3_gemm_issue_rz_bf16 runs on it, instead of decoding per tile
+ * inside the GEMM.  Same arguments, same results, still driven by the records on the device
+ * (two launches that return at once when the records are empty); several times faster when
+ * hundreds or thousands of rows are listed.  No reference counterpart beyond that of
+ * ue5m3_gemm_fp4_fallback.
+ */
+size_t ue5m3_fallback_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int ue5m3_gemm_fp4_fallback_ws(const uint8_t *a_codes, const uint8_t *a_sf_raw, const int *a_record,
+                               const uint8_t *b_codes, const uint8_t *b_sf_raw,
+                               const int *b_record, int64_t M, int64_t N, int64_t K, int snap,
+                               const float *alpha_dev, const float *amax_a_dev,
+                               const float *amax_b_dev, float inv_denominator, const void *bias,
+                               int bias_dtype, void *out, int out_dtype, int64_t ldo,
+                               void *workspace, size_t workspace_bytes, int *status_dev,
+                               void *stream);
+
+/*
  * Test hook: compares the software E2M1 ties-to-even rounding with the sm_100a
  * cvt.rn.satfinite.e2m1x2.f32 instruction over `count` consecutive fp32 bit
  * patterns starting at `first_bits`; mismatch_count_dev[0] receives the number

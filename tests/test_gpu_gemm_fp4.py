@@ -1,6 +1,6 @@
 """The FP4 block-scaled tensor-core GEMM (ue5m3_gemm_fp4) and its scale packer, through the
 C ABI: scale-factor layout against a numpy restatement, the window records of scales outside
-UE4M3's range and the recomputation they drive (ue5m3_gemm_fp4_fallback), bit-exactness
+UE4M3's range and the recomputation they drive (ue5m3_gemm_fp4_fallback[_ws]), bit-exactness
 against the oracle on packed operands, equality with the BF16-issue kernel, and the
 benchmark shapes on sampled rows x columns."""
 
@@ -22,6 +22,16 @@ def b200():
 
     assert module.available()
     return module
+
+
+@pytest.fixture(autouse=True, params=["workspace", "inline"])
+def recomputation_mode(request, monkeypatch):
+    """Every test runs with both forms of the recomputation pass: operands decoded once into a
+    workspace for the TMA-fed issue-RZ kernel (ue5m3_gemm_fp4_fallback_ws, the default) and
+    decoded per tile inside the pass's own kernel (ue5m3_gemm_fp4_fallback)."""
+
+    monkeypatch.setenv("UE5M3_FALLBACK", request.param)
+    return request.param
 
 
 def _expected_scale_layout(scales: np.ndarray, rows: int, k: int, block: int, two_d: bool, shift: int,
@@ -644,3 +654,39 @@ def test_launches_after_a_recorded_failure_mark_their_output(b200):
     torch.cuda.synchronize()
     b200.check_gemm_status(dev)
     assert bool(torch.isfinite(healthy).all())
+
+
+def test_workspace_form_checks_its_workspace(b200):
+    """ue5m3_gemm_fp4_fallback_ws: the size function is (2 x list capacity + M + N) rows of K bf16
+    values, and a workspace that is missing, too small or misaligned is refused before anything
+    is launched."""
+
+    from ue5m3_fp4 import _native as native
+
+    lib = native.load()
+    m, n, k = 192, 320, 256
+    need = lib.ue5m3_fallback_workspace_bytes(m, n, k)
+    assert need == (2 * b200.FALLBACK_MAX_ROWS + m + n) * k * 2
+    assert lib.ue5m3_fallback_workspace_bytes(0, n, k) == 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(3)
+    amax = torch.ones(1, device=dev) * 8.0
+    ops = [b200.quantize_fp4_operand(torch.randn(r, k, generator=g).to(torch.bfloat16).cuda(), block_size=16,
+                                     blocking=b200.BLOCK_ROW, transposed=False, tensor_amax=amax, scale_target=448.0)
+           for r in (m, n)]
+    out = torch.zeros(m, n, device=dev)
+    workspace = torch.empty(need + 16, dtype=torch.uint8, device=dev)
+
+    def call(ws_ptr, ws_bytes):
+        a, b = ops
+        return lib.ue5m3_gemm_fp4_fallback_ws(
+            a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(), b.codes.data_ptr(),
+            b.raw_scale_factors.data_ptr(), b.record.data_ptr(), m, n, k, 1, None, None, None, 0.0, None, 0,
+            out.data_ptr(), 1, n, ws_ptr, ws_bytes, None, native.stream_ptr(dev))
+
+    assert call(None, need) == 1                               # invalid argument
+    assert call(workspace.data_ptr(), need - 1) == 1
+    assert call(workspace.data_ptr() + 8, need) == 3           # alignment
+    assert call(workspace.data_ptr(), need) == 0               # empty records: two launches that return at once
+    torch.cuda.synchronize()
+    assert not out.any()

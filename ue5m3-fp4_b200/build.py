@@ -14,7 +14,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 SOURCES = ["abi.cu", "amax.cu", "quantize.cu", "quantize_operand.cu", "gemm_sm100.cu", "gemm_fp4_sm100.cu",
-           "gemm_fallback.cu", "window_place.cu"]
+           "gemm_fallback.cu", "fallback_workspace.cu", "window_place.cu"]
 OUTPUT = HERE / "lib" / "libue5m3_b200.so"
 
 

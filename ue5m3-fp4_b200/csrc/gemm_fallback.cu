@@ -33,6 +33,7 @@
 
 #include "abi_common.cuh"
 #include "alpha_spec.cuh"
+#include "decode_bf16.cuh"
 #include "tcgen05_ptx.cuh"
 #include "ue5m3_device.cuh"
 #include "window_record.cuh"
@@ -68,6 +69,7 @@ struct Params {
     const uint8_t* raw_b;
     const int* rec_a;
     const int* rec_b;
+    int jobs;                 // bit 0: listed rows of A, bit 1: listed rows of B, bit 2: whole product after an overflow
 };
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -110,14 +112,6 @@ struct Tile {
     int rows, cols;     // extent of the job's output
 };
 
-// prmt.b32 as the hardware defines it: bit 3 of a selector nibble replicates the selected byte's
-// top bit over the result byte (the __byte_perm intrinsic promises the low three bits only).
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
-    return d;
-}
-
 // Barrier `id` of the CTA over `threads` threads: waiting warps take no issue slots, unlike
 // warps polling an mbarrier.  Every thread of the group must arrive.
 __device__ __forceinline__ void group_sync(int id, int threads) {
@@ -140,44 +134,6 @@ __device__ __forceinline__ bool group_wait(bool poller, int id, int threads, vol
     return *word != 0;
 }
 
-// A UE5M3 scale byte as a bf16 pair (both halves the same).  A normal byte E<<3|M is the bf16
-// (E + 112) << 7 | M << 4; the seven subnormal bytes take the slow way; byte 0 (an all-zero
-// block, or padding) gives 0.
-__device__ __forceinline__ uint32_t scale_pair(uint32_t scale_byte) {
-    uint32_t bits = (scale_byte << 4) + 0x3800u;
-    if (scale_byte < 8u) bits = __bfloat16_as_ushort(__float2bfloat16_rn(ue5m3_decode(scale_byte)));
-    return __byte_perm(bits, bits, 0x1010);
-}
-
-// Eight codes (one 32-bit word) x one scale -> eight bf16 values, in registers only.  A byte
-// permute is a four-way lookup in an eight-byte table, which is exactly an E2M1 magnitude (3
-// bits) -> one byte of its bf16 encoding: two permutes give the high bytes of eight codes, two
-// the low bytes.  The sign bit of a code is bit 3 of its nibble, which a permute's selector reads
-// as "replicate the selected byte's top bit": over a table of 0x80 bytes that yields 0xFF for a
-// negative code and 0x80 otherwise, and bit 6 of that byte, moved up by one, is the bf16 sign.
-// The packed multiply by the scale is exact (a 2-bit by a 4-bit significand).
-__device__ __forceinline__ uint4 decode_word(uint32_t word, uint32_t scale2_bits) {
-    constexpr uint32_t kHighA = 0x3F3F3F00u, kHighB = 0x40404040u;   // 0 .5 1 1.5 | 2 3 4 6
-    constexpr uint32_t kLowA = 0xC0800000u, kLowB = 0xC0804000u;
-    const uint32_t mag = word & 0x77777777u;
-    const uint32_t word_hi = word >> 16, mag_hi = mag >> 16;
-    uint32_t high0 = prmt(kHighA, kHighB, mag), low0 = prmt(kLowA, kLowB, mag);
-    uint32_t high1 = prmt(kHighA, kHighB, mag_hi), low1 = prmt(kLowA, kLowB, mag_hi);
-    const uint32_t neg0 = prmt(0x80808080u, 0x80808080u, word & 0xFFFFu);
-    const uint32_t neg1 = prmt(0x80808080u, 0x80808080u, word_hi);
-    high0 |= (neg0 << 1) & 0x80808080u;
-    high1 |= (neg1 << 1) & 0x80808080u;
-    const uint32_t pairs[4] = {__byte_perm(low0, high0, 0x5140), __byte_perm(low0, high0, 0x7362),
-                               __byte_perm(low1, high1, 0x5140), __byte_perm(low1, high1, 0x7362)};
-    const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&scale2_bits);
-    uint32_t out[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 product = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pairs[i]), scale2);
-        out[i] = *reinterpret_cast<const uint32_t*>(&product);
-    }
-    return make_uint4(out[0], out[1], out[2], out[3]);
-}
 
 template <typename OutT>
 __device__ __forceinline__ OutT to_out(float v);
@@ -193,7 +149,6 @@ __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return
 template <int BN>
 struct Pass {
     static constexpr int kBN = BN;
-    static constexpr bool kRowPass = BN == 32;     // which of the three products this instance computes
     static constexpr int kStages = BN == 32 ? 10 : 6;
     static constexpr int kProducerWarps = BN == 32 ? 10 : 7;   // 16 warps in all either way: register files are handed out per four warps
     static constexpr int kCols = BN == 32 ? 32 : 64;   // columns per epilogue warp
@@ -206,16 +161,16 @@ struct Pass {
     static constexpr uint32_t kStageBytesB = kBN * kBK * 2;
     static constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
 
-    static __device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, int M, int N) {
+    static __device__ __forceinline__ Plan make_plan(const int* rec_a, const int* rec_b, int M, int N, int jobs) {
         Plan plan;
         const int na = __ldg(rec_a + kRecListed), nb = __ldg(rec_b + kRecListed);
         plan.full = na > kRecMaxRows || nb > kRecMaxRows;
         plan.na = plan.full ? 0 : na;
         plan.nb = plan.full ? 0 : nb;
         const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + kBN - 1) / kBN;
-        plan.tiles[0] = kRowPass ? ((plan.na + kBM - 1) / kBM) * tiles_n : 0;
-        plan.tiles[1] = kRowPass ? 0 : tiles_m * ((plan.nb + kBN - 1) / kBN);
-        plan.tiles[2] = (!kRowPass && plan.full) ? tiles_m * tiles_n : 0;
+        plan.tiles[0] = (jobs & 1) ? ((plan.na + kBM - 1) / kBM) * tiles_n : 0;
+        plan.tiles[1] = (jobs & 2) ? tiles_m * ((plan.nb + kBN - 1) / kBN) : 0;
+        plan.tiles[2] = ((jobs & 4) && plan.full) ? tiles_m * tiles_n : 0;
         return plan;
     }
 
@@ -346,7 +301,7 @@ struct Pass {
     }
 
     static __device__ __forceinline__ void run(const Params& p) {
-        const Plan plan = make_plan(p.rec_a, p.rec_b, p.M, p.N);
+        const Plan plan = make_plan(p.rec_a, p.rec_b, p.M, p.N, p.jobs);
         const int total_tiles = plan.tiles[0] + plan.tiles[1] + plan.tiles[2];
         if ((int)blockIdx.x >= total_tiles) return;  // the whole CTA, before anything is set up
 
@@ -592,8 +547,10 @@ extern "C" int ue5m3_gemm_fp4_fallback(const uint8_t* a_codes, const uint8_t* a_
     p.rec_a = a_record; p.rec_b = b_record;
     // two launches, both driven by the records on the device: the listed rows of A (narrow tiles),
     // then the listed rows of B and, after a list overflow, the whole product (wide tiles)
+    p.jobs = 1;
     const int status_rows = fb::launch_pass<32>(p, static_cast<cudaStream_t>(stream_v));
     if (status_rows != UE5M3_OK) return status_rows;
+    p.jobs = 2 | 4;
     const int status_cols = fb::launch_pass<128>(p, static_cast<cudaStream_t>(stream_v));
     if (status_cols != UE5M3_OK) return status_cols;
     return check_launch();

@@ -28,6 +28,7 @@
 
 #include "abi_common.cuh"
 #include "alpha_spec.cuh"
+#include "issue_rz_mapped.cuh"
 #include "dead_fill.cuh"
 
 namespace ue5m3 {
@@ -56,6 +57,17 @@ struct GemmParams {
     long long ldo;
     int* status;
     int tiles_m, tiles_n;
+    // Mapped launches only (the recomputation pass of the FP4 product, on operands decoded into a
+    // workspace): the kernel gets four operand buffers - the listed rows of A and of B gathered
+    // (map_a, map_b; capacity valid_cap rows) and A and B in full (map_a_full, map_b_full; M and N
+    // rows) - and walks the tiles of up to three products: listed A x full B -> output rows
+    // row_map[i]; full A x listed B -> output columns col_map[i]; full A x full B when a list
+    // overflowed (a count above valid_cap).  The counts are read on the device.
+    const int* valid_m;
+    const int* valid_n;
+    int valid_cap;
+    const int* row_map;
+    const int* col_map;
 };
 
 struct __align__(8) GemmBarriers {
@@ -234,10 +246,35 @@ __device__ __forceinline__ float rint_rne(float v) {
     return copysignf(r, v);
 }
 
+// Epilogue stores of a mapped launch: one thread's 128 finished values (after snap and alpha)
+// of A row `row`, B rows col0 .. col0 + 127, to out[row_map[row]][col_map[col]] with the bias of
+// the output column.
+__device__ __forceinline__ void store_mapped_row(const GemmParams& p, float (&c)[kBN / 2], long long row, int col0,
+                                                 int lim_n, const int* row_map, const int* col_map) {
+    const long long out_row = row_map ? (long long)__ldg(row_map + row) : row;
+#pragma unroll
+    for (int i = 0; i < kBN / 2; ++i) {
+        const int col = col0 + i;
+        if (col >= lim_n) continue;
+        const int out_col = col_map ? __ldg(col_map + col) : col;
+        float v = c[i];
+        if (p.bias)
+            v = __fadd_rn(v, p.bias_dtype == UE5M3_DTYPE_BF16
+                                 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[out_col])
+                                 : static_cast<const float*>(p.bias)[out_col]);
+        if (p.out_dtype == UE5M3_DTYPE_BF16)
+            static_cast<__nv_bfloat16*>(p.out)[out_row * p.ldo + out_col] = __float2bfloat16_rn(v);
+        else
+            static_cast<float*>(p.out)[out_row * p.ldo + out_col] = v;
+    }
+}
+
 // ---- kernel ----------------------------------------------------------------
+template <bool kMapped>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
-                     const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_a_full, const __grid_constant__ CUtensorMap map_b_full,
+                     const GemmParams p) {
     extern __shared__ unsigned char smem_dyn[];
     // 1024-byte alignment for the 128-byte swizzle atoms
     unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -248,17 +285,47 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
     const int lane = threadIdx.x & 31;
     const int num_issues = p.K / kBK;
 
-    // grouped raster: 8 tile rows share each sweep over tile columns
-    constexpr int kGroupM = 8;
-    const int tile = blockIdx.x;
-    const int tiles_per_group = kGroupM * p.tiles_n;
-    const int group = tile / tiles_per_group;
-    const int first_m = group * kGroupM;
-    const int group_m = (p.tiles_m - first_m) < kGroupM ? (p.tiles_m - first_m) : kGroupM;
-    const int tile_m = first_m + (tile % tiles_per_group) % group_m;
-    const int tile_n = (tile % tiles_per_group) / group_m;
-    const int m0 = tile_m * kBM;
-    const int n0 = tile_n * kBN;
+    // Plain launches: one tile per CTA, grouped raster (8 tile rows share each sweep over tile
+    // columns).  Mapped launches: persistent CTAs walk the tiles of the rectangle of rows that
+    // exist (known on the device only); the issue counter runs on across tiles, so the mbarrier
+    // phases never need re-initialising.
+    int first_tile = blockIdx.x, num_tiles = blockIdx.x + 1, tile_step = 1;
+    int job_rows[3] = {0, 0, 0}, job_cols[3] = {0, 0, 0}, job_first[4] = {0, 0, 0, 0};   // mapped launches
+    if (kMapped) {
+        const int na = __ldg(p.valid_m), nb = __ldg(p.valid_n);
+        const bool overflow = na > p.valid_cap || nb > p.valid_cap;
+        job_rows[0] = overflow ? 0 : na; job_cols[0] = p.N;               // listed A x full B
+        job_rows[1] = p.M;               job_cols[1] = overflow ? 0 : nb;  // full A x listed B
+        job_rows[2] = overflow ? p.M : 0; job_cols[2] = p.N;              // full A x full B
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const int tiles = job_rows[j] > 0 && job_cols[j] > 0
+                                  ? ((job_rows[j] + kBM - 1) / kBM) * ((job_cols[j] + kBN - 1) / kBN) : 0;
+            job_first[j + 1] = job_first[j] + tiles;
+        }
+        num_tiles = job_first[3];
+        tile_step = gridDim.x;
+        if ((int)blockIdx.x >= num_tiles) return;   // the whole CTA, before anything is set up
+    }
+    // tile -> origin in its product's own row / column numbering (and which product)
+    auto tile_origin = [&](int tile, int& m0, int& n0) -> int {
+        if (kMapped) {
+            const int job = tile < job_first[1] ? 0 : (tile < job_first[2] ? 1 : 2);
+            const int local = tile - job_first[job];
+            const int tiles_n = (job_cols[job] + kBN - 1) / kBN;
+            m0 = (local / tiles_n) * kBM;
+            n0 = (local % tiles_n) * kBN;
+            return job;
+        }
+        constexpr int kGroupM = 8;
+        const int tiles_per_group = kGroupM * p.tiles_n;
+        const int group = tile / tiles_per_group;
+        const int first_m = group * kGroupM;
+        const int group_m = (p.tiles_m - first_m) < kGroupM ? (p.tiles_m - first_m) : kGroupM;
+        m0 = (first_m + (tile % tiles_per_group) % group_m) * kBM;
+        n0 = ((tile % tiles_per_group) / group_m) * kBN;
+        return 0;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -282,137 +349,175 @@ gemm_issue_rz_kernel(const __grid_constant__ CUtensorMap map_a,
 
     if (dead) {
         // no work after a recorded failure: mark this CTA's tile and fall through to the common exit
-        fill_tile_nan(p.out, p.out_dtype == UE5M3_DTYPE_BF16, p.ldo, m0, n0, kBM, kBN, p.M, p.N);
+        // (a mapped launch rewrites parts of an output that the preceding FP4 launch has marked)
+        if (!kMapped) {
+            int m0, n0;
+            tile_origin(first_tile, m0, n0);
+            fill_tile_nan(p.out, p.out_dtype == UE5M3_DTYPE_BF16, p.ldo, m0, n0, kBM, kBN, p.M, p.N);
+        }
     } else if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int j = 0; j < num_issues; ++j) {
-                const int s = j % kStages;
-                const uint32_t use = j / kStages;
-                if (use > 0 && !mbar_wait(&bars->empty[s], (use - 1) & 1, bars, p.status, 1, j)) break;
-                unsigned char* sa = smem + s * kStageBytes;
-                unsigned char* sb = sa + kStageBytesA;
-                mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
-                tma_load_2d(sa, &map_a, &bars->full[s], j * kBK, m0);
-                tma_load_2d(sb, &map_b, &bars->full[s], j * kBK, n0);
+            int g = 0;   // issues since the kernel started
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                int m0, n0;
+                const int job = tile_origin(tile, m0, n0);
+                const CUtensorMap* tile_a = (kMapped && job != 0) ? &map_a_full : &map_a;
+                const CUtensorMap* tile_b = (kMapped && job != 1) ? &map_b_full : &map_b;
+                for (int j = 0; j < num_issues; ++j, ++g) {
+                    const int s = g % kStages;
+                    const uint32_t use = g / kStages;
+                    if (use > 0 && !mbar_wait(&bars->empty[s], (use - 1) & 1, bars, p.status, 1, j)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* sa = smem + s * kStageBytes;
+                    unsigned char* sb = sa + kStageBytesA;
+                    mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
+                    tma_load_2d(sa, tile_a, &bars->full[s], j * kBK, m0);
+                    tma_load_2d(sb, tile_b, &bars->full[s], j * kBK, n0);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(kBM, kBN);
-            for (int j = 0; j < num_issues; ++j) {
-                const int s = j % kStages;
-                const int b = j & 1;
-                const uint32_t use_b = j >> 1;
-                if (use_b > 0 && !mbar_wait(&bars->tmem_empty[b], (use_b - 1) & 1, bars, p.status, 2, j)) break;
-                if (!mbar_wait(&bars->full[s], (j / kStages) & 1, bars, p.status, 3, j)) break;
-                tcgen05_fence_after();
-                const uint32_t sa = smem_u32(smem + s * kStageBytes);
-                const uint32_t sb = sa + kStageBytesA;
-                const uint64_t desc_a = make_smem_desc(sa);
-                const uint64_t desc_b = make_smem_desc(sb);
-                const uint32_t tmem_d = tmem_base + (uint32_t)b * kBN;
+            int g = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                for (int j = 0; j < num_issues; ++j, ++g) {
+                    const int s = g % kStages;
+                    const int b = g & 1;
+                    const uint32_t use_b = g >> 1;
+                    if (use_b > 0 && !mbar_wait(&bars->tmem_empty[b], (use_b - 1) & 1, bars, p.status, 2, j)) {
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&bars->full[s], (g / kStages) & 1, bars, p.status, 3, j)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * kStageBytes);
+                    const uint32_t sb = sa + kStageBytesA;
+                    const uint64_t desc_a = make_smem_desc(sa);
+                    const uint64_t desc_b = make_smem_desc(sb);
+                    const uint32_t tmem_d = tmem_base + (uint32_t)b * kBN;
 #pragma unroll
-                for (int k = 0; k < kBK / kUmmaK; ++k) {
-                    // advance 16 bf16 = 32 bytes inside the swizzle atom: +2 in 16-byte units
-                    umma_bf16(tmem_d, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
-                              k > 0 ? 1u : 0u);
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // advance 16 bf16 = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                        umma_bf16(tmem_d, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                                  k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&bars->empty[s]);      // smem stage reusable once the MMAs have read it
+                    umma_commit(&bars->tmem_full[b]);  // issue partial complete in TMEM
                 }
-                umma_commit(&bars->empty[s]);      // smem stage reusable once the MMAs have read it
-                umma_commit(&bars->tmem_full[b]);  // issue partial complete in TMEM
             }
         }
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;            // TMEM lane quadrant
         const int h = (warp - 2) >> 2;     // column half of the tile
-        float c[kBN / 2];
-#pragma unroll
-        for (int i = 0; i < kBN / 2; ++i) c[i] = 0.0f;
+        int g = 0;
         bool ok = true;
-        for (int j = 0; j < num_issues; ++j) {
-            const int b = j & 1;
-            ok = mbar_wait(&bars->tmem_full[b], (j >> 1) & 1, bars, p.status, 4, j);
-            ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for tcgen05.ld
-            if (!ok) break;
-            tcgen05_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * (kBN / 2));
-            // two 32-column loads in flight per wait; packed round-toward-zero adds
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+            int m0, n0;
+            const int job = tile_origin(tile, m0, n0);
+            const int lim_m = kMapped ? job_rows[job] : p.M;
+            const int lim_n = kMapped ? job_cols[job] : p.N;
+            float c[kBN / 2];
 #pragma unroll
-            for (int half = 0; half < kBN / 2 / 64; ++half) {
-                uint32_t v0[32], v1[32];
-                tmem_load_32_async(taddr + half * 64, v0);
-                tmem_load_32_async(taddr + half * 64 + 32, v1);
-                tmem_wait_ld();
+            for (int i = 0; i < kBN / 2; ++i) c[i] = 0.0f;
+            for (int j = 0; j < num_issues; ++j, ++g) {
+                const int b = g & 1;
+                ok = mbar_wait(&bars->tmem_full[b], (g >> 1) & 1, bars, p.status, 4, j);
+                ok = __all_sync(0xFFFFFFFFu, ok);  // keep the warp convergent for tcgen05.ld
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kBN + h * (kBN / 2));
+                // two 32-column loads in flight per wait; packed round-toward-zero adds
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    fadd2_rz(c[half * 64 + i], c[half * 64 + i + 1], v0[i], v0[i + 1]);
-                    fadd2_rz(c[half * 64 + 32 + i], c[half * 64 + 33 + i], v1[i], v1[i + 1]);
+                for (int half = 0; half < kBN / 2 / 64; ++half) {
+                    uint32_t v0[32], v1[32];
+                    tmem_load_32_async(taddr + half * 64, v0);
+                    tmem_load_32_async(taddr + half * 64 + 32, v1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        fadd2_rz(c[half * 64 + i], c[half * 64 + i + 1], v0[i], v0[i + 1]);
+                        fadd2_rz(c[half * 64 + 32 + i], c[half * 64 + 33 + i], v1[i], v1[i + 1]);
+                    }
                 }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-        }
-        if (ok) {
-            const float alpha = alpha_value(p.alpha);
-            const bool scale_by_alpha = alpha_enabled(p.alpha);
-            const long long row = (long long)m0 + q * 32 + lane;
-            const int col0 = n0 + h * (kBN / 2);
-            if (row < p.M) {
-#pragma unroll
-                for (int i = 0; i < kBN / 2; ++i) {
-                    float v = c[i];
-                    if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
-                    if (scale_by_alpha) v = __fmul_rn(v, alpha);
-                    c[i] = v;
-                }
-                if (p.bias) {
+            if (ok) {
+                const float alpha = alpha_value(p.alpha);
+                const bool scale_by_alpha = alpha_enabled(p.alpha);
+                const long long row = (long long)m0 + q * 32 + lane;
+                const int col0 = n0 + h * (kBN / 2);
+                if (row < lim_m) {
 #pragma unroll
                     for (int i = 0; i < kBN / 2; ++i) {
-                        int col = col0 + i;
-                        if (col < p.N) {
-                            float bv = p.bias_dtype == UE5M3_DTYPE_BF16
-                                           ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
-                                           : static_cast<const float*>(p.bias)[col];
-                            c[i] = __fadd_rn(c[i], bv);
-                        }
+                        float v = c[i];
+                        if (p.snap) v = __fmul_rn(rint_rne(__fmul_rn(v, 1024.0f)), 0.0009765625f);
+                        if (scale_by_alpha) v = __fmul_rn(v, alpha);
+                        c[i] = v;
                     }
                 }
-                if (p.out_dtype == UE5M3_DTYPE_BF16) {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
-                    const bool vec = (p.ldo % 8) == 0 && ((uintptr_t)p.out % 16) == 0;
+                if (kMapped) {
+                    if (row < lim_m)
+                        store_mapped_row(p, c, row, col0, lim_n, job == 0 ? p.row_map : nullptr, job == 1 ? p.col_map : nullptr);
+                } else if (row < p.M) {
+                    if (p.bias) {
 #pragma unroll
-                    for (int i = 0; i < kBN / 2; i += 8) {
-                        if (vec && col0 + i + 8 <= p.N) {
-                            uint4 w;
-                            w.x = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 0])) |
-                                  ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 1])) << 16);
-                            w.y = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 2])) |
-                                  ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 3])) << 16);
-                            w.z = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 4])) |
-                                  ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 5])) << 16);
-                            w.w = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 6])) |
-                                  ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 7])) << 16);
-                            *reinterpret_cast<uint4*>(out + i) = w;
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (col0 + i + e < p.N) out[i + e] = __float2bfloat16_rn(c[i + e]);
+                        for (int i = 0; i < kBN / 2; ++i) {
+                            int col = col0 + i;
+                            if (col < p.N) {
+                                float bv = p.bias_dtype == UE5M3_DTYPE_BF16
+                                               ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col])
+                                               : static_cast<const float*>(p.bias)[col];
+                                c[i] = __fadd_rn(c[i], bv);
+                            }
                         }
                     }
-                } else {
-                    float* out = static_cast<float*>(p.out) + row * p.ldo + col0;
-                    const bool vec = (p.ldo % 4) == 0 && ((uintptr_t)p.out % 16) == 0;
+                    if (p.out_dtype == UE5M3_DTYPE_BF16) {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+                        const bool vec = (p.ldo % 8) == 0 && ((uintptr_t)p.out % 16) == 0;
 #pragma unroll
-                    for (int i = 0; i < kBN / 2; i += 4) {
-                        if (vec && col0 + i + 4 <= p.N) {
-                            *reinterpret_cast<float4*>(out + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
-                        } else {
+                        for (int i = 0; i < kBN / 2; i += 8) {
+                            if (vec && col0 + i + 8 <= p.N) {
+                                uint4 w;
+                                w.x = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 0])) |
+                                      ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 1])) << 16);
+                                w.y = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 2])) |
+                                      ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 3])) << 16);
+                                w.z = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 4])) |
+                                      ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 5])) << 16);
+                                w.w = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 6])) |
+                                      ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c[i + 7])) << 16);
+                                *reinterpret_cast<uint4*>(out + i) = w;
+                            } else {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col0 + i + e < p.N) out[i + e] = c[i + e];
+                                for (int e = 0; e < 8; ++e)
+                                    if (col0 + i + e < p.N) out[i + e] = __float2bfloat16_rn(c[i + e]);
+                            }
+                        }
+                    } else {
+                        float* out = static_cast<float*>(p.out) + row * p.ldo + col0;
+                        const bool vec = (p.ldo % 4) == 0 && ((uintptr_t)p.out % 16) == 0;
+#pragma unroll
+                        for (int i = 0; i < kBN / 2; i += 4) {
+                            if (vec && col0 + i + 4 <= p.N) {
+                                *reinterpret_cast<float4*>(out + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (col0 + i + e < p.N) out[i + e] = c[i + e];
+                            }
                         }
                     }
                 }
@@ -467,6 +572,34 @@ static int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, in
     return UE5M3_OK;
 }
 
+// The mapped launch (issue_rz_mapped.cuh).
+int launch_issue_rz_mapped(const MappedOperands& ops, int64_t M, int64_t N, int64_t K, int snap, const AlphaSpec& alpha,
+                           const void* bias, int bias_dtype, void* out, int out_dtype, int64_t ldo, int* status_dev,
+                           cudaStream_t stream) {
+    const int64_t tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + kBN - 1) / kBN;
+    if (tiles_m * tiles_n > 0x7FFFFFFF) return UE5M3_ERR_TOO_LARGE;
+    CUtensorMap map_a, map_b, map_a_full, map_b_full;
+    int status = make_operand_map(&map_a, ops.a_listed, ops.cap, K, kBM);
+    if (status == UE5M3_OK) status = make_operand_map(&map_b, ops.b_listed, ops.cap, K, kBN);
+    if (status == UE5M3_OK) status = make_operand_map(&map_a_full, ops.a_full, M, K, kBM);
+    if (status == UE5M3_OK) status = make_operand_map(&map_b_full, ops.b_full, N, K, kBN);
+    if (status != UE5M3_OK) return status;
+    GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.snap = snap ? 1 : 0;
+    p.alpha = alpha;
+    p.bias = bias; p.bias_dtype = bias_dtype;
+    p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.status = status_dev;
+    p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
+    p.valid_m = ops.a_count; p.valid_n = ops.b_count; p.valid_cap = ops.cap;
+    p.row_map = ops.a_list; p.col_map = ops.b_list;
+    const size_t smem = (size_t)kStages * kStageBytes + sizeof(GemmBarriers) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_issue_rz_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    // persistent CTAs (one per SM at most): with nothing listed every one of them returns at once
+    gemm_issue_rz_kernel<true><<<sm_count(), kNumThreads, smem, stream>>>(map_a, map_b, map_a_full, map_b_full, p);
+    return UE5M3_OK;
+}
+
 }  // namespace ue5m3
 
 using namespace ue5m3;
@@ -502,10 +635,11 @@ extern "C" int ue5m3_gemm_issue_rz_bf16(const void* a, const void* bt, int64_t M
     p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n;
 
     const size_t smem = (size_t)kStages * kStageBytes + sizeof(GemmBarriers) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_issue_rz_kernel,
+    p.valid_m = nullptr; p.valid_n = nullptr; p.valid_cap = 0; p.row_map = nullptr; p.col_map = nullptr;
+    cudaError_t e = cudaFuncSetAttribute(gemm_issue_rz_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return record_cuda_error(e);
-    gemm_issue_rz_kernel<<<(unsigned)(tiles_m * tiles_n), kNumThreads, smem,
-                           static_cast<cudaStream_t>(stream_v)>>>(map_a, map_b, p);
+    gemm_issue_rz_kernel<false><<<(unsigned)(tiles_m * tiles_n), kNumThreads, smem,
+                                  static_cast<cudaStream_t>(stream_v)>>>(map_a, map_b, map_a, map_b, p);
     return check_launch();
 }

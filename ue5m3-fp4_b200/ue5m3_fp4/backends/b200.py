@@ -756,6 +756,34 @@ def window_log_summary() -> dict:
     return summary
 
 
+def fallback_mode() -> str:
+    """"workspace" (default): the recomputation pass decodes every needed operand row once into a
+    per-stream device workspace and runs the TMA-fed issue-RZ kernel on it; "inline"
+    (UE5M3_FALLBACK=inline): it decodes per tile inside its own GEMM kernel and needs no memory."""
+
+    import os
+
+    mode = os.environ.get("UE5M3_FALLBACK", "workspace").strip().lower()
+    if mode not in ("workspace", "inline"):
+        raise ValueError("UE5M3_FALLBACK must be 'workspace' or 'inline'")
+    return mode
+
+
+_fallback_workspaces: dict[tuple[torch.device, int], Tensor] = {}
+
+
+def _fallback_workspace(device: torch.device, size: int) -> Tensor:
+    """Grow-only scratch of the recomputation pass, one per (device, stream): calls on one stream
+    are ordered, so consecutive products share it."""
+
+    key = (device, _native.stream_ptr(device) or 0)
+    held = _fallback_workspaces.get(key)
+    if held is None or held.numel() < size:
+        held = torch.empty(size, dtype=torch.uint8, device=device)
+        _fallback_workspaces[key] = held
+    return held
+
+
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None,
                       bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
     """FP4 tensor-core product of two packed operands, followed (stream-ordered, no host
@@ -773,16 +801,22 @@ def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tenso
     out = gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
                    shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype,
                    a_record=a.record, b_record=b.record)
-    with torch.cuda.device(out.device):
-        status = _native.load().ue5m3_gemm_fp4_fallback(
-            a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(),
-            b.codes.data_ptr(), b.raw_scale_factors.data_ptr(), b.record.data_ptr(),
-            a.rows, b.rows, a.k, int(bool(snap)), *_alpha_arguments(alpha, out.device), _native.ptr(bias),
+    lib = _native.load()
+    tail = (a.rows, b.rows, a.k, int(bool(snap)), *_alpha_arguments(alpha, out.device), _native.ptr(bias),
             _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
-            _native.dtype_code(out_dtype), b.rows, gemm_status(out.device).data_ptr(),
-            _native.stream_ptr(out.device),
-        )
-    _native.check(status, "ue5m3_gemm_fp4_fallback", launches=2)   # one launch per tile width
+            _native.dtype_code(out_dtype), b.rows)
+    operands = (a.codes.data_ptr(), a.raw_scale_factors.data_ptr(), a.record.data_ptr(),
+                b.codes.data_ptr(), b.raw_scale_factors.data_ptr(), b.record.data_ptr())
+    with torch.cuda.device(out.device):
+        if fallback_mode() == "workspace":
+            workspace = _fallback_workspace(out.device, lib.ue5m3_fallback_workspace_bytes(a.rows, b.rows, a.k))
+            status = lib.ue5m3_gemm_fp4_fallback_ws(*operands, *tail, workspace.data_ptr(), workspace.numel(),
+                                                    gemm_status(out.device).data_ptr(), _native.stream_ptr(out.device))
+            _native.check(status, "ue5m3_gemm_fp4_fallback_ws", launches=2)   # decode, then one GEMM launch for all lists
+        else:
+            status = lib.ue5m3_gemm_fp4_fallback(*operands, *tail, gemm_status(out.device).data_ptr(),
+                                                 _native.stream_ptr(out.device))
+            _native.check(status, "ue5m3_gemm_fp4_fallback", launches=2)   # one launch per tile width
     if _window_log is not None:
         _window_log.append((a.record, b.record, (a.rows, b.rows, a.k)))
     return out
