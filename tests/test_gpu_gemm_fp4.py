@@ -686,7 +686,7 @@ def test_workspace_form_checks_its_workspace(b200):
 
     assert call(None, need) == 1                               # invalid argument
     assert call(workspace.data_ptr(), need - 1) == 1
-    assert call(workspace.data_ptr() + 8, need) == 3           # alignment
+    assert call(workspace.data_ptr() + 8, need) == 4           # alignment
     assert call(workspace.data_ptr(), need) == 0               # empty records: two launches that return at once
     torch.cuda.synchronize()
     assert not out.any()
