@@ -33,6 +33,7 @@ M, K, N = 8192, 4096, 21504
 BLOCK = 16
 TARGET = 448.0
 REFRESH_INTERVAL = 50
+BUCKET_MB = int(os.environ.get("UE5M3_BENCH_BUCKET_MB", "200"))   # DDP gradient bucket size of the c5 leg
 METRIC = "probe_matched_fp4_gemm_tflops_m8192_k4096_n21504"
 UNIT = "TFLOP/s"
 WORKLOAD = "forward probe-matched GEMM Y=X.W^T, X bf16 8192x4096 N(0,1), W bf16 21504x4096 N(0,0.02^2), B=16"
@@ -567,7 +568,7 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         wrapped = model
         if world > 1:
             wrapped = DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True,
-                                              bucket_cap_mb=200, broadcast_buffers=False)
+                                              bucket_cap_mb=BUCKET_MB, broadcast_buffers=False)
         # learning rate 0: the optimizer step runs in full (same kernels, same memory traffic) but the
         # weights keep the statistics of their random initialisation, so that the synthetic
         # activations and gradients do not drift toward whatever a repeated random batch rewards
@@ -623,7 +624,7 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
             "what": "Nemotron-H-8B-shaped stack (52 layers, 112 FP4 linears B=16 at their real shapes, stand-in mixers, "
                     "FP32 head with TF32 matmul), uniform random token ids drawn per step, seq 8192, micro-batch 1 per GPU, "
                     "forward + backward + fused AdamW (bf16 parameters and optimizer state, learning rate 0), torch DDP, "
-                    "bf16 gradient buckets of 200 MB",
+                    f"bf16 gradient buckets of {BUCKET_MB} MB",
             "tokens_per_s": seq * world / (hold_ms * 1e-3), "ms_hold_step": hold_ms, "ms_refresh_step": refresh_ms,
             "tokens_per_s_refresh_step": seq * world / (refresh_ms * 1e-3),
             "ms_hold_step_without_gradient_allreduce": local_ms,
