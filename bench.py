@@ -302,16 +302,20 @@ class HotPath:
             wq = ops.quantize_packed(self.w, block_size=BLOCK, blocking=ops.BLOCK_2D, tensor_amax=self.amax_w,
                                      scale_target=TARGET, packed=False, packed_t=False, fake_domain="encoded",
                                      fake_dtype=torch.bfloat16).fake
+        events = None
         if time_gemm:
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
+            events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self.gemm_events.append(events)
         if self.path == "fp4":
-            y = ops.gemm_fp4_operands(xq, wq, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
+            # the events bracket the FP4 GEMM launch alone: the placement before it and the
+            # recomputation pass after it are separate kernels of the step
+            y = ops.gemm_fp4_operands(xq, wq, snap=True, alpha=alpha, out_dtype=torch.bfloat16, kernel_events=events)
         else:
+            if events:
+                events[0].record()
             y = ops.gemm_issue_rz(xq, wq, snap=True, alpha=alpha, out_dtype=torch.bfloat16)
-        if time_gemm:
-            stop.record()
-            self.gemm_events.append((start, stop))
+            if events:
+                events[1].record()
         return y
 
     def step_e2e(self):

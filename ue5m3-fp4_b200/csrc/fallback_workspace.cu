@@ -41,7 +41,7 @@ struct DecodeArgs {
 // An item is 32 consecutive elements of one operand row: 16 bytes of codes and two scale bytes
 // in, 64 bytes out.  Four sections, walked with one grid-stride loop: A's listed rows, all of B
 // (if A lists any), B's listed rows, all of A (if B lists any).
-__global__ void __launch_bounds__(256) decode_operands_kernel(const DecodeArgs d) {
+__global__ void __launch_bounds__(512) decode_operands_kernel(const DecodeArgs d) {
     int listed[2];
 #pragma unroll
     for (int o = 0; o < 2; ++o) listed[o] = __ldg(d.rec[o] + kRecListed);
@@ -117,7 +117,8 @@ extern "C" int ue5m3_gemm_fp4_fallback_ws(const uint8_t* a_codes, const uint8_t*
     d.listed[1] = d.listed[0] + (size_t)kRecMaxRows * K;
     d.full[0] = d.listed[1] + (size_t)kRecMaxRows * K;
     d.full[1] = d.full[0] + (size_t)M * K;
-    fb::decode_operands_kernel<<<sm_count() * 8, 256, 0, stream>>>(d);
+    // few, large CTAs: with nothing listed (the usual case) the launch costs what its CTAs cost to start
+    fb::decode_operands_kernel<<<sm_count() * 2, 512, 0, stream>>>(d);
 
     MappedOperands ops{d.listed[0], d.listed[1], d.full[0], d.full[1], kRecMaxRows, a_record + kRecListed,
                        b_record + kRecListed, a_record + kRecHeader, b_record + kRecHeader};

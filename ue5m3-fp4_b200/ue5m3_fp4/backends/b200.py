@@ -785,22 +785,28 @@ def _fallback_workspace(device: torch.device, size: int) -> Tensor:
 
 
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None,
-                      bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> Tensor:
+                      bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32,
+                      kernel_events: "tuple[torch.cuda.Event, torch.cuda.Event] | None" = None) -> Tensor:
     """FP4 tensor-core product of two packed operands, followed (stream-ordered, no host
     synchronisation) by the recomputation of whatever their window records list: output rows
     for A, output columns for B, everything when a list overflowed.  The recomputation runs the
     issue-RZ BF16 instruction sequence on the exact encoded operands, so the result is the
     reference model's for every UE5M3 scale (the reference has no scale window,
-    formats.py:125-134)."""
+    formats.py:125-134).  ``kernel_events``: a (start, stop) pair recorded directly around the FP4
+    GEMM launch itself, for measurements of that kernel alone."""
 
     if a.k != b.k:
         raise ValueError("a and b have incompatible K dimensions")
     if a.record is None or b.record is None or a.raw_scale_factors is None or b.raw_scale_factors is None:
         raise ValueError("packed operands must carry their raw scales and window records")
     place_row_windows(a, b)
+    if kernel_events is not None:
+        kernel_events[0].record()
     out = gemm_fp4(a.codes, a.scale_factors, b.codes, b.scale_factors, m=a.rows, n=b.rows, k=a.k,
                    shift_sum=a.shift + b.shift, snap=snap, alpha=alpha, bias=bias, out_dtype=out_dtype,
                    a_record=a.record, b_record=b.record)
+    if kernel_events is not None:
+        kernel_events[1].record()
     lib = _native.load()
     tail = (a.rows, b.rows, a.k, int(bool(snap)), *_alpha_arguments(alpha, out.device), _native.ptr(bias),
             _native.dtype_code(bias.dtype) if bias is not None else 0, out.data_ptr(),
