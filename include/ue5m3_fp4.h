@@ -271,6 +271,21 @@ int ue5m3_quantize_fp4_operand_t(const void *x, int dtype, int64_t rows, int64_t
                                  void *stream);
 
 /*
+ * A weight in both orientations from one read: x [rows, cols] with B x B blocks
+ * (UE5M3_BLOCK_2D), ties-to-even -> the operand x (codes [rows, cols/2], its atoms, raw atoms
+ * and window record) AND the operand x^T (codes_t [cols, rows/2], ...), i.e. what
+ * ue5m3_quantize_fp4_operand and ue5m3_quantize_fp4_operand_t write, bit for bit: B x B blocks
+ * have the same scale in both orientations (formats.py:294-328), so the forward GEMM's W and the
+ * data-gradient GEMM's W^T of one training step (nn/linear.py:312-313,359-363 of the reference
+ * re-quantize the weight for each) come out of one launch.  rows % 64 == 0 and cols % 64 == 0.
+ */
+int ue5m3_quantize_fp4_operand_both(const void *x, int dtype, int64_t rows, int64_t cols, int block,
+                                    const float *amax_dev, float target, int shift,
+                                    uint8_t *codes, uint8_t *sf, uint8_t *sf_raw,
+                                    int *window_record, uint8_t *codes_t, uint8_t *sf_t,
+                                    uint8_t *sf_raw_t, int *window_record_t, void *stream);
+
+/*
  * The weight-gradient operands of the TE-settings comparator (nn/linear.py:23-40,80-114,
  * 389-400): the operand is x^T with the fixed-sign, normalized B=16 Hadamard transform applied
  * along its reduction axis (the rows of x) before 16 x 1 block quantization.

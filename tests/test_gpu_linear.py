@@ -326,6 +326,7 @@ def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monk
 
     tokens, in_f, out_f = 1024, 2048, 384
     results = {}
+    monkeypatch.setenv("UE5M3_WEIGHT_BOTH", "0")   # the weight's second operand is a saved tensor of its own
     for mode in ("1", "0"):
         monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
         monkeypatch.setenv("UE5M3_SAVE_PACKED_ACTIVATIONS", mode)
@@ -356,6 +357,45 @@ def test_packed_activation_saving_keeps_gradients_and_shrinks_what_is_saved(monk
     bf16_extra = results["0"][3] - weight_bytes
     assert bf16_extra == tokens * in_f * 2
     assert packed_extra * 3 < bf16_extra
+
+
+def test_weight_quantized_once_per_step_keeps_gradients(monkeypatch):
+    """By default the forward pass makes both operands of the weight (W for Y = X W^T, W^T for
+    dX = dY W) in one launch and hands W^T to backward; with UE5M3_WEIGHT_BOTH=0 backward
+    quantizes the weight again as the reference does.  Same outputs and gradients, bit for bit;
+    the saved W^T operand costs 0.5625 + 0.0625 byte per weight element until backward has run."""
+
+    import ue5m3_fp4.nn.linear as linear_module
+
+    tokens, in_f, out_f = 256, 320, 192
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("UE5M3_GEMM_PATH", "fp4")
+        monkeypatch.setenv("UE5M3_WEIGHT_BOTH", mode)
+        layer = _layer(in_f, out_f, bias=True, seed=6)
+        layer.scale_state.begin_step(1)
+        draws = []
+
+        def fixed_bits(reference, draws=draws):
+            bits = random_bits(reference.shape, seed=70 + len(draws), dtype=torch.uint8).to(reference.device)
+            draws.append(bits)
+            return bits
+
+        monkeypatch.setattr(linear_module, "_draw_bits", fixed_bits)
+        g = torch.Generator().manual_seed(4)
+        x = torch.randn(tokens, in_f, generator=g).to(torch.bfloat16).cuda().requires_grad_(True)
+        dy = (1e-3 * torch.randn(tokens, out_f, generator=g)).to(torch.bfloat16).cuda()
+        saved = []
+        with torch.autograd.graph.saved_tensors_hooks(lambda t: (saved.append(t.numel() * t.element_size()), t)[1],
+                                                      lambda t: t):
+            y = layer(x)
+        y.backward(dy)
+        torch.cuda.synchronize()
+        results[mode] = (y.detach().clone(), x.grad.clone(), layer.weight.grad.clone(), layer.bias.grad.clone(), sum(saved))
+    for a, b in zip(results["1"][:4], results["0"][:4]):
+        assert torch.equal(a, b)
+    extra = results["1"][4] - results["0"][4]
+    assert out_f * in_f * 0.625 <= extra <= out_f * in_f * 0.625 + 4 * (4 + 4096 + 2 * in_f) + 4096
 
 
 def test_frozen_weight_operand_is_built_once_in_inference(monkeypatch):

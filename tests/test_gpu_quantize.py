@@ -350,3 +350,34 @@ def test_philox_stream_definition(b200):
         words = _philox4x32_10([unit, 0, stream & 0xFFFFFFFF, stream >> 32], [seed & 0xFFFFFFFF, seed >> 32])
         expect = np.array(words, dtype=np.uint32).view(np.uint8)
         assert np.array_equal(raw[16 * unit:16 * unit + 16], expect), unit
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols,block", [(128, 128, 16), (192, 320, 16), (448, 64, 32), (256, 384, 32)])
+def test_weight_operands_of_both_orientations_from_one_launch(b200, dtype, rows, cols, block):
+    """ue5m3_quantize_fp4_operand_both: W and W^T as packed GEMM operands from one read of a weight
+    with B x B blocks equal, bit for bit, what the two single-orientation quantizers write -
+    codes, tensor-core scale atoms, raw scale atoms and window records, including all-zero blocks
+    and blocks whose scale leaves the tensor core's range."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(rows + cols + block)
+    w = 0.02 * torch.randn(rows, cols, generator=g)
+    w[:16, :16] = 0.0                       # an all-zero block
+    w[32:64, cols // 2:] *= 2.0 ** -22      # scales far below the window at this shift
+    w[5, 3] = 1.5                           # the amax, well above everything else
+    w = w.to(dtype).cuda()
+    amax = b200.tensor_amax(w).reshape(1)
+    both = b200.quantize_fp4_operand_both(w, block_size=block, tensor_amax=amax, scale_target=448.0, shift_headroom=1)
+    assert both is not None
+    for operand, transposed in zip(both, (False, True)):
+        single = b200.quantize_fp4_operand(w, block_size=block, blocking=b200.BLOCK_2D, transposed=transposed,
+                                           tensor_amax=amax, scale_target=448.0, shift_headroom=1)
+        assert (operand.rows, operand.k, operand.shift) == (single.rows, single.k, single.shift)
+        assert torch.equal(operand.codes, single.codes)
+        assert torch.equal(operand.scale_factors, single.scale_factors)
+        assert torch.equal(operand.raw_scale_factors, single.raw_scale_factors)
+        assert operand.window_counts() == single.window_counts() and operand.window_counts()[0] > 0
+        assert sorted(operand.flagged_rows()) == sorted(single.flagged_rows())
+    assert b200.quantize_fp4_operand_both(w[:, :40].contiguous(), block_size=block, tensor_amax=amax,
+                                          scale_target=448.0) is None

@@ -254,6 +254,11 @@ struct OperandTArgs {
     int shift;
     int* window_record;   // see include/ue5m3_fp4.h
     unsigned int* transformed_amax;  // amax-only mode: max |transformed value| as fp32 bits
+    // BOTH mode (2-D blocks, ties-to-even): the operand x itself as well, from the same tile
+    uint8_t* codes;       // [rows, cols / 2]
+    uint8_t* sf;          // atoms of the [rows, cols] operand
+    uint8_t* sf_raw;
+    int* window_record_rows;
 };
 
 // The fixed-sign, normalized B=16 Hadamard transform of the TE-settings comparator
@@ -305,11 +310,15 @@ __device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch
     }
 }
 
-template <typename T, int B, bool TWO_D, int RMODE, int BITS, bool RHT, bool AMAX_ONLY>
+template <typename T, int B, bool TWO_D, int RMODE, int BITS, bool RHT, bool AMAX_ONLY, bool BOTH = false>
 __global__ void __launch_bounds__(
-    256, RMODE == kRoundTteHw ? 4 : ((RMODE == kRoundSr && sizeof(T) == 2 && B == 16 && !TWO_D && !RHT) ? 3 : 2))
+    256, (RMODE == kRoundTteHw && !BOTH) ? 4 : ((RMODE == kRoundSr && sizeof(T) == 2 && B == 16 && !TWO_D && !RHT) ? 3 : 2))
 quantize_operand_t_kernel(const OperandTArgs a) {
     static_assert(!RHT || (B == 16 && !TWO_D), "the transform is defined on 16 x 1 blocks");
+    static_assert(!BOTH || (TWO_D && !RHT && !AMAX_ONLY && RMODE != kRoundSr),
+                  "both orientations share scales only for B x B blocks; weights round ties-to-even");
+    // BOTH: scale code (and 0 for an all-zero block) of every B x B block of the tile, for phase 3
+    __shared__ uint8_t block_code[kTT / 16][kTT / 16], block_raw[kTT / 16][kTT / 16];
     constexpr bool kSr = RMODE == kRoundSr;
     constexpr int kPitch = TransposeTile<T>::kPitch;
     constexpr int kChunksPerRow = TransposeTile<T>::kWordsPerRow / 4;  // 16-byte chunks
@@ -440,6 +449,11 @@ quantize_operand_t_kernel(const OperandTArgs a) {
             uint32_t code;
             float scale;
             block_scale_converged(m[h][j], ts, code, scale);
+            if (BOTH && j == 0 && (lane % (B / 2)) == 0 && (B == 16 || h == 0)) {
+                const int rb = (row_base + 16 * h) / B, cb = (ch * 64 + 2 * lane) / B;
+                block_code[rb][cb] = (uint8_t)code;
+                block_raw[rb][cb] = m[h][j] == 0.0f ? (uint8_t)0 : (uint8_t)code;
+            }
             bool outside;
             sf_pair[j] |= ue4m3_window_byte(code, rebias, outside) << (8 * h);
             raw_pair[j] |= (m[h][j] == 0.0f ? 0u : code) << (8 * h);   // 0 marks an all-zero block
@@ -491,6 +505,70 @@ quantize_operand_t_kernel(const OperandTArgs a) {
         }
     }
     window_record_units(a.window_record, bad_units);
+
+    // ---- phase 3 (BOTH): the operand x itself from the same tile.  Thread = one row x 64
+    // columns (one atom word): the block scales are those of phase 2 (B x B blocks are the same
+    // in both orientations), the payload arithmetic is quantize_operand_kernel's.
+    if (BOTH) {
+        __syncthreads();
+        const int prow = tid >> 1, half = tid & 1;
+        const int64_t grow = r0 + prow, gcol0 = c0 + half * 64;
+        int bad_rows = 0;
+        if (gcol0 < a.cols) {   // cols % 64 == 0: a 64-column half is in or out
+            const bool valid = grow < a.rows;
+            uint32_t sf_bytes = 0u, raw_bytes = 0u;
+            uint32_t packed[4][2];
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                const uint32_t code = block_code[prow / B][(half * 64 + blk * 16) / B];
+                bool outside;
+                sf_bytes |= ue4m3_window_byte(code, rebias, outside) << (8 * blk);
+                raw_bytes |= (uint32_t)block_raw[prow / B][(half * 64 + blk * 16) / B] << (8 * blk);
+                if (outside && valid) {
+                    ++bad_rows;
+                    window_record_row(a.window_record_rows, grow);
+                }
+                const float rcp = payload_multiplier(ue5m3_decode(code), ts);
+                float v[16];
+                if (sizeof(T) == 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t w = tile[prow * kPitch + (half * 64 + blk * 16) / 2 + i];
+                        v[2 * i] = __uint_as_float(w << 16);
+                        v[2 * i + 1] = __uint_as_float(w & 0xFFFF0000u);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(tile[prow * kPitch + half * 64 + blk * 16 + i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) mul2_rn(v[i], v[i + 1], rcp);
+#pragma unroll
+                for (int h8 = 0; h8 < 2; ++h8) {
+                    float w8[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) w8[i] = v[h8 * 8 + i];
+                    if (RMODE == kRoundTteHw) {
+                        packed[blk][h8] = e2m1_pack8_hw(w8);
+                    } else {
+                        packed[blk][h8] = 0u;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) packed[blk][h8] += e2m1_nibble<false>(w8[i], 0u) * (1u << (4 * i));
+                    }
+                }
+            }
+            if (valid) {
+                uint4* dst = reinterpret_cast<uint4*>(a.codes + grow * (a.cols / 2) + gcol0 / 2);
+                dst[0] = make_uint4(packed[0][0], packed[0][1], packed[1][0], packed[1][1]);
+                dst[1] = make_uint4(packed[2][0], packed[2][1], packed[3][0], packed[3][1]);
+            }
+            // the tile spans one whole 128-row group of this operand too: rows beyond `rows` get 1.0
+            const int64_t word = (((grow >> 7) * (a.cols / 64) + gcol0 / 64) * 128 + (grow & 31) * 4 + ((grow >> 5) & 3)) * 4;
+            *reinterpret_cast<uint32_t*>(a.sf + word) = valid ? sf_bytes : 0x38383838u;
+            if (a.sf_raw) *reinterpret_cast<uint32_t*>(a.sf_raw + word) = valid ? raw_bytes : 0u;
+        }
+        window_record_units(a.window_record_rows, bad_rows);
+    }
 }
 
 template <typename T, int B, bool TWO_D, bool RHT>
@@ -536,6 +614,7 @@ int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols
     args.bits = bits; args.codes_t = codes_t; args.sf_t = sf_t; args.sf_raw_t = sf_raw_t; args.shift = shift;
     args.window_record = window_record;
     args.transformed_amax = nullptr;
+    args.codes = nullptr; args.sf = nullptr; args.sf_raw = nullptr; args.window_record_rows = nullptr;
     const int rmode = sr ? kRoundSr : (use_hw_cvt() ? kRoundTteHw : kRoundTteSw);
     const bool two_d = blocking == UE5M3_BLOCK_2D;
     int status;
@@ -555,9 +634,58 @@ int quantize_operand_t_fast(const void* x, int dtype, int64_t rows, int64_t cols
     return check_launch();
 }
 
+// 2-D blocks, ties-to-even: x [rows, cols] -> both GEMM operands (x and x^T) in one launch.
+template <typename T, int B>
+static void launch_operand_both(const OperandTArgs& args, int rmode, cudaStream_t stream) {
+    dim3 grid((unsigned)((args.cols + kTT - 1) / kTT), (unsigned)((args.rows + kTT - 1) / kTT));
+    const size_t smem = (size_t)kTT * TransposeTile<T>::kPitch * 4;
+    if (rmode == kRoundTteHw) {
+        auto kernel = quantize_operand_t_kernel<T, B, true, kRoundTteHw, UE5M3_BITS_U8, false, false, true>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, 256, smem, stream>>>(args);
+    } else {
+        auto kernel = quantize_operand_t_kernel<T, B, true, kRoundTteSw, UE5M3_BITS_U8, false, false, true>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, 256, smem, stream>>>(args);
+    }
+}
+
 }  // namespace ue5m3
 
 using namespace ue5m3;
+
+extern "C" int ue5m3_quantize_fp4_operand_both(const void* x, int dtype, int64_t rows, int64_t cols, int block,
+                                               const float* amax_dev, float target, int shift, uint8_t* codes,
+                                               uint8_t* sf, uint8_t* sf_raw, int* window_record, uint8_t* codes_t,
+                                               uint8_t* sf_t, uint8_t* sf_raw_t, int* window_record_t,
+                                               void* stream_v) {
+    if (!x || !amax_dev || !codes || !sf || !window_record || !codes_t || !sf_t || !window_record_t || rows <= 0 || cols <= 0)
+        return UE5M3_ERR_INVALID_ARGUMENT;
+    if (dtype != UE5M3_DTYPE_BF16 && dtype != UE5M3_DTYPE_FP32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (block != 16 && block != 32) return UE5M3_ERR_INVALID_ARGUMENT;
+    if (!(target > 0.0f) || shift < -8 || shift > 16) return UE5M3_ERR_INVALID_ARGUMENT;
+    if ((rows % 64) || (cols % 64)) return UE5M3_ERR_K_NOT_DIVISIBLE;   // both orientations are GEMM operands
+    if (rows > 0x7FFFFFFF || cols > 0x7FFFFFFF || (rows + kTT - 1) / kTT > 65535) return UE5M3_ERR_TOO_LARGE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)codes % 16) || ((uintptr_t)codes_t % 16) || ((uintptr_t)sf % 4) ||
+        ((uintptr_t)sf_t % 4) || ((uintptr_t)sf_raw % 4) || ((uintptr_t)sf_raw_t % 4))
+        return UE5M3_ERR_ALIGNMENT;
+    OperandTArgs args;
+    args.x = x; args.rows = rows; args.cols = cols; args.amax_dev = amax_dev;
+    args.six_t = (float)((double)target * 6.0);
+    args.bits = nullptr; args.codes_t = codes_t; args.sf_t = sf_t; args.sf_raw_t = sf_raw_t; args.shift = shift;
+    args.window_record = window_record_t; args.transformed_amax = nullptr;
+    args.codes = codes; args.sf = sf; args.sf_raw = sf_raw; args.window_record_rows = window_record;
+    const int rmode = use_hw_cvt() ? kRoundTteHw : kRoundTteSw;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (dtype == UE5M3_DTYPE_BF16) {
+        if (block == 16) launch_operand_both<__nv_bfloat16, 16>(args, rmode, stream);
+        else launch_operand_both<__nv_bfloat16, 32>(args, rmode, stream);
+    } else {
+        if (block == 16) launch_operand_both<float, 16>(args, rmode, stream);
+        else launch_operand_both<float, 32>(args, rmode, stream);
+    }
+    return check_launch();
+}
 
 extern "C" int ue5m3_quantize_fp4_operand(const void* x, int dtype, int64_t rows, int64_t cols,
                                           int block, int blocking, const float* amax_dev,

@@ -93,6 +93,8 @@ def load() -> ctypes.CDLL:
     lib.ue5m3_gemm_fp4_fallback_ws.restype = i32
     lib.ue5m3_gemm_fp4_fallback_ws.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, p, p, p, f32, p, i32, p, i32, i64,
                                                p, ctypes.c_size_t, p, p]
+    lib.ue5m3_quantize_fp4_operand_both.restype = i32
+    lib.ue5m3_quantize_fp4_operand_both.argtypes = [p, i32, i64, i64, i32, p, f32, i32, p, p, p, p, p, p, p, p, p]
     lib.ue5m3_philox_bytes.restype = i32
     lib.ue5m3_philox_bytes.argtypes = [p, i64, p, p]
     lib.ue5m3_gemm_fp4.restype = i32

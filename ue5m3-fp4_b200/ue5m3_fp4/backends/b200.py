@@ -571,6 +571,43 @@ def quantize_fp4_operand(
     return Fp4Operand(codes, sf, shift, rows, k, raw, record)
 
 
+def quantize_fp4_operand_both(x: Tensor, *, block_size: int, tensor_amax: Tensor, scale_target: float,
+                              shift_headroom: int = 0) -> "tuple[Fp4Operand, Fp4Operand] | None":
+    """A weight ``x`` [R, C] with B x B blocks, ties-to-even, as BOTH packed GEMM operands from
+    one read: (operand of x, reduction over C; operand of x^T, reduction over R) - bit for bit
+    what two ``quantize_fp4_operand`` calls give (ue5m3_quantize_fp4_operand_both).  Returns None
+    when the shape does not qualify (both dimensions multiples of 64, contiguous, aligned); the
+    caller then makes the two operands separately."""
+
+    _require_cuda(x, "x")
+    if x.ndim != 2 or x.shape[0] % 64 or x.shape[1] % 64 or not x.is_contiguous() or x.data_ptr() % 16:
+        return None
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        return None
+    if tensor_amax.device != x.device or tensor_amax.dtype is not torch.float32 or tensor_amax.numel() != 1:
+        raise ValueError("tensor_amax must be a one-element float32 tensor on the operand's device")
+    if block_size not in (16, 32):
+        raise ValueError("block_size must be 16 or 32")
+    shift = scale_shift_for_target(scale_target) + shift_headroom
+    rows, cols = x.shape
+    dev = x.device
+    lib = _native.load()
+    codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    codes_t = torch.empty((cols, rows // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty(lib.ue5m3_packed_scales_bytes(rows, cols), dtype=torch.uint8, device=dev)
+    sf_t = torch.empty(lib.ue5m3_packed_scales_bytes(cols, rows), dtype=torch.uint8, device=dev)
+    raw, raw_t = torch.empty_like(sf), torch.empty_like(sf_t)
+    record, record_t = new_window_record(rows, dev), new_window_record(cols, dev)
+    with torch.cuda.device(dev):
+        status = lib.ue5m3_quantize_fp4_operand_both(
+            x.data_ptr(), _native.dtype_code(x.dtype), rows, cols, block_size, tensor_amax.data_ptr(),
+            float(scale_target), shift, codes.data_ptr(), sf.data_ptr(), raw.data_ptr(), record.data_ptr(),
+            codes_t.data_ptr(), sf_t.data_ptr(), raw_t.data_ptr(), record_t.data_ptr(), _native.stream_ptr(dev))
+    _native.check(status, "ue5m3_quantize_fp4_operand_both")
+    return (Fp4Operand(codes, sf, shift, rows, cols, raw, record),
+            Fp4Operand(codes_t, sf_t, shift, cols, rows, raw_t, record_t))
+
+
 def _quantize_fp4_operand_fused(x: Tensor, block_size: int, blocking: int, tensor_amax: Tensor,
                                 scale_target: float, rounding, random_bits: Tensor | None, shift: int,
                                 *, want_scales: bool = False, transposed: bool = False, hadamard: bool = False):

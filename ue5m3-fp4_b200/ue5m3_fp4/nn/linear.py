@@ -61,6 +61,15 @@ def _finite_amax(tensor: torch.Tensor) -> torch.Tensor:
     return sample_global_amax(tensor, label="UE5M3 operand amax")
 
 
+def _weight_operands_in_one_launch() -> bool:
+    """UE5M3_WEIGHT_BOTH=0 makes backward quantize W^T again (as the reference does) instead of
+    taking it from the forward pass's single read of the weight."""
+
+    import os
+
+    return os.environ.get("UE5M3_WEIGHT_BOTH", "1") != "0"
+
+
 def _save_packed_activations() -> bool:
     """Save the packed weight-gradient operand of X instead of the bf16 activations
     (UE5M3_SAVE_PACKED_ACTIVATIONS=0 keeps the bf16 copy, as the reference does)."""
@@ -294,6 +303,19 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         x_enc = _encode_k_major(x, plan=plan, role="activation", reference=activation_reference,
                                 reduce_over_rows=False, two_dimensional=False)
         w_enc = owner._packed_frozen_weight(weight, weight_reference, plan) if owner._inference["active"] else None
+        wt_enc = None
+        if (w_enc is None and two_d and plan.path == "fp4" and ctx.needs_input_grad[0] and _weight_operands_in_one_launch()
+                and not owner._inference["active"] and owner.__dict__.get("_scale_histograms") is None
+                and plan.rounding("weight") is RoundingMode.TIES_TO_EVEN):
+            # The data-gradient GEMM of this step reads W^T with the same B x B block scales: both
+            # orientations leave one launch that reads W once (the reference quantizes the weight
+            # again in backward, linear.py:359-363).  W^T travels to backward as saved tensors.
+            from ue5m3_fp4.backends import b200
+
+            both = b200.quantize_fp4_operand_both(w, block_size=plan.block, tensor_amax=weight_reference.reshape(1),
+                                                  scale_target=plan.target("weight"), shift_headroom=1)
+            if both is not None:
+                w_enc, wt_enc = both
         if w_enc is None:
             w_enc = _encode_k_major(w, plan=plan, role="weight", reference=weight_reference,
                                     reduce_over_rows=False, two_dimensional=two_d)
@@ -325,9 +347,14 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
                                  reference=activation_rht_reference if rht else activation_reference,
                                  reduce_over_rows=True, two_dimensional=False, hadamard=rht)
             ctx.packed_activation = (xt.shift, xt.rows, xt.k)
-            ctx.save_for_backward(weight, xt.codes, xt.scale_factors, xt.raw_scale_factors, xt.record)
+            saved = [weight, xt.codes, xt.scale_factors, xt.raw_scale_factors, xt.record]
         else:
-            ctx.save_for_backward(weight, inputs)
+            saved = [weight, inputs]
+        ctx.packed_weight_t = None
+        if wt_enc is not None:
+            ctx.packed_weight_t = (wt_enc.shift, wt_enc.rows, wt_enc.k, len(saved))
+            saved += [wt_enc.codes, wt_enc.scale_factors, wt_enc.raw_scale_factors, wt_enc.record]
+        ctx.save_for_backward(*saved)
         return output.reshape(*inputs.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -339,15 +366,21 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
 
         plan = _OperandPlan(owner)
         two_d = owner.recipe.two_dimensional_weights
+        saved = ctx.saved_tensors
+        weight = saved[0]
         if ctx.packed_activation is not None:
-            weight, xt_codes, xt_scales, xt_raw_scales, xt_record = ctx.saved_tensors
+            xt_codes, xt_scales, xt_raw_scales, xt_record = saved[1:5]
             shift, rows, k = ctx.packed_activation
             xt_saved = b200.Fp4Operand(xt_codes, xt_scales, shift, rows, k, xt_raw_scales, xt_record)
             x = None
         else:
-            weight, inputs = ctx.saved_tensors
+            inputs = saved[1]
             xt_saved = None
             x = inputs.to(torch.bfloat16).reshape(-1, inputs.shape[-1]).contiguous()
+        wt_saved = None
+        if ctx.packed_weight_t is not None:
+            shift, rows, k, first = ctx.packed_weight_t
+            wt_saved = b200.Fp4Operand(saved[first], saved[first + 1], shift, rows, k, saved[first + 2], saved[first + 3])
         dy = grad_output.to(torch.bfloat16).reshape(-1, grad_output.shape[-1]).contiguous()
         w = weight.detach().contiguous()
 
@@ -357,8 +390,8 @@ class _ProbeMatchedUE5M3LinearFunction(torch.autograd.Function):
         # dX[M,K] = dY[M,N] . W[N,K]: reduce over N; W is read with N contiguous -> transpose
         dy_enc = _encode_k_major(dy, plan=plan, role="upstream_gradient", reference=dy_reference,
                                  reduce_over_rows=False, two_dimensional=False)
-        wt_enc = _encode_k_major(w, plan=plan, role="weight", reference=ctx.weight_reference,
-                                 reduce_over_rows=True, two_dimensional=two_d)
+        wt_enc = wt_saved if wt_saved is not None else _encode_k_major(
+            w, plan=plan, role="weight", reference=ctx.weight_reference, reduce_over_rows=True, two_dimensional=two_d)
         grad_input = _gemm(
             dy_enc, wt_enc, owner=owner, reference_a=dy_reference, reference_b=ctx.weight_reference,
             target_a=plan.target("upstream_gradient"), target_b=plan.target("weight"),
