@@ -17,6 +17,12 @@
 // TMEM owner, warps 2..9 = epilogue (TMEM lane quadrant = warp % 4, column
 // half = (warp - 2) / 4).
 //
+// Two instantiations.  Plain: one CTA per tile of a product of two bf16 operands
+// (ue5m3_gemm_issue_rz_bf16).  Mapped: persistent CTAs walk the tiles of the up to three
+// products of the FP4 path's recomputation pass - operands that fallback_workspace.cu has
+// decoded into a workspace, extents and row / column lists read on the device - with the issue
+// counter running on across tiles (issue_rz_mapped.cuh).
+//
 // Every wait is bounded by a clock budget; on expiry the kernel records where
 // it gave up in the caller's status words, raises a CTA-wide abort flag and
 // falls through to the common exit, where TMEM is released.
