@@ -115,7 +115,7 @@ quantize_operand_kernel(const OperandArgs a) {
             raw_bytes |= (m[u] == 0.0f ? 0u : code[u]) << (8 * u);   // 0 marks an all-zero block
             if (outside && valid && a.sf) {
                 ++bad_units;
-                window_record_row(a.window_record, row);
+                window_record_row_cold(a.window_record, row);
             }
             const float rcp = payload_multiplier(scale, ts);
             float v[16];
@@ -312,7 +312,8 @@ __device__ __forceinline__ void tile_pair_values(const uint32_t* tile, int pitch
 
 template <typename T, int B, bool TWO_D, int RMODE, int BITS, bool RHT, bool AMAX_ONLY, bool BOTH = false>
 __global__ void __launch_bounds__(
-    256, (RMODE == kRoundTteHw && !BOTH) ? 4 : ((RMODE == kRoundSr && sizeof(T) == 2 && B == 16 && !TWO_D && !RHT) ? 3 : 2))
+    256, (RMODE == kRoundTteHw && !BOTH) ? 4
+                                         : (((RMODE == kRoundSr && sizeof(T) == 2 && B == 16 && !TWO_D && !RHT) || (BOTH && sizeof(T) == 2)) ? 3 : 2))
 quantize_operand_t_kernel(const OperandTArgs a) {
     static_assert(!RHT || (B == 16 && !TWO_D), "the transform is defined on 16 x 1 blocks");
     static_assert(!BOTH || (TWO_D && !RHT && !AMAX_ONLY && RMODE != kRoundSr),
@@ -459,7 +460,7 @@ quantize_operand_t_kernel(const OperandTArgs a) {
             raw_pair[j] |= (m[h][j] == 0.0f ? 0u : code) << (8 * h);   // 0 marks an all-zero block
             if (outside && rows_valid && col + j < a.cols) {
                 ++bad_units;
-                window_record_row(a.window_record, col + j);
+                window_record_row_cold(a.window_record, col + j);
             }
             const float rcp = payload_multiplier(scale, ts);
 #pragma unroll
@@ -526,7 +527,7 @@ quantize_operand_t_kernel(const OperandTArgs a) {
                 raw_bytes |= (uint32_t)block_raw[prow / B][(half * 64 + blk * 16) / B] << (8 * blk);
                 if (outside && valid) {
                     ++bad_rows;
-                    window_record_row(a.window_record_rows, grow);
+                    window_record_row_cold(a.window_record_rows, grow);
                 }
                 const float rcp = payload_multiplier(ue5m3_decode(code), ts);
                 float v[16];

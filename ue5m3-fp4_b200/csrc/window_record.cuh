@@ -30,6 +30,10 @@ __device__ __forceinline__ void window_record_row(int* rec, int64_t row) {
     if (*((volatile int*)flag) == 0 && atomicExch(flag, 1) == 0) atomicAdd(rec + kRecFlagged, 1);
 }
 
+// The same as a call: for the quantizers' inner loops, where the flagging is rare and its inlined
+// atomics would cost every thread registers.
+static __device__ __noinline__ void window_record_row_cold(int* rec, int64_t row) { window_record_row(rec, row); }
+
 // Adds a thread's count of out-of-window 16-element units, one atomic per warp at most.
 __device__ __forceinline__ void window_record_units(int* rec, int units) {
     if (!__any_sync(0xFFFFFFFFu, units != 0)) return;
