@@ -412,7 +412,24 @@ def new_window_record(rows: int, device: torch.device) -> Tensor:
     """Zeroed window record of an operand with ``rows`` rows (layout: include/ue5m3_fp4.h): the
     quantizer lists here the rows that hold a block scale outside the tensor core's UE4M3 range."""
 
-    return torch.zeros(_native.load().ue5m3_window_record_ints(rows), dtype=torch.int32, device=device)
+    count = _native.load().ue5m3_window_record_ints(rows)
+    padded = (count + 3) & ~3   # slices stay 16-byte aligned
+    if padded > _RECORD_CHUNK_INTS // 4:
+        return torch.zeros(count, dtype=torch.int32, device=device)
+    # Records are small and needed by the dozen per layer step: they are cut from a zeroed chunk
+    # (one fill launch per chunk instead of one per record).  A chunk belongs to one stream, so
+    # its fill is ordered before every kernel that uses a slice; an exhausted chunk lives on for
+    # as long as any of its slices does.
+    key = (device, _native.stream_ptr(device) or 0)
+    chunk, used = _record_chunks.get(key, (None, 0))
+    if chunk is None or used + padded > chunk.numel():
+        chunk, used = torch.zeros(_RECORD_CHUNK_INTS, dtype=torch.int32, device=device), 0
+    _record_chunks[key] = (chunk, used + padded)
+    return chunk[used:used + count]
+
+
+_RECORD_CHUNK_INTS = 1 << 22   # 16 MiB
+_record_chunks: dict[tuple[torch.device, int], tuple[Tensor, int]] = {}
 
 
 def scale_shift_for_target(scale_target: float) -> int:
