@@ -690,3 +690,34 @@ def test_workspace_form_checks_its_workspace(b200):
     assert call(workspace.data_ptr(), need) == 0               # empty records: two launches that return at once
     torch.cuda.synchronize()
     assert not out.any()
+
+
+def test_recomputation_walks_more_tiles_than_there_are_sms(b200, monkeypatch):
+    """Every row of A listed (five row tiles) against 10240 columns, and some hundred rows of B
+    listed as well: each persistent CTA of the recomputation pass walks several tiles, of two
+    products, with an odd number of K=64 issues per tile - so the running issue counter has to
+    carry the pipeline's barrier phases from tile to tile.  Equal, bit for bit, to the BF16-issue
+    product of the same operands."""
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(21)
+    m, k, n = 640, 192, 10240
+    a = torch.randn(m, k, generator=g)
+    a[:, 32:48] *= 2.0 ** -22            # every row of A spans more than the window
+    a = a.to(torch.bfloat16)
+    bt = torch.randn(n, k, generator=g)
+    bt[::31, 64:80] *= 2.0 ** -22        # 331 rows of B as well
+    bt = bt.to(torch.bfloat16)
+    amax_a = torch.tensor([float(a.float().abs().max())], device=dev)
+    amax_b = torch.tensor([float(bt.float().abs().max())], device=dev)
+    op_a = b200.quantize_fp4_operand(a.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=amax_a, scale_target=448.0)
+    op_b = b200.quantize_fp4_operand(bt.cuda(), block_size=16, blocking=b200.BLOCK_ROW, transposed=False,
+                                     tensor_amax=amax_b, scale_target=448.0)
+    alpha = b200.encoded_global_alpha(amax_a, amax_b, 448.0, 448.0)
+    got = b200.gemm_fp4_operands(op_a, op_b, snap=True, alpha=alpha)
+    torch.cuda.synchronize()
+    b200.check_gemm_status(dev)
+    assert op_a.record[2].item() == m and op_b.record[2].item() == len(range(0, n, 31))
+    expect = _bf16_path_product(b200, a, bt, block=16, two_d=False, amax_a=amax_a, amax_b=amax_b, monkeypatch=monkeypatch)
+    assert torch.equal(got, expect)
