@@ -565,6 +565,9 @@ def _c5_training_step(torch, dist, device, rank: int, world: int, local_rank: in
         model = NemotronHShapedStack(device=device, dtype=torch.bfloat16)
         model.lm_head.to(torch.float32)  # the vocabulary head keeps FP32 parameters
         conversion = convert_reported_nemotron_h(model)
+        from ue5m3_fp4.nn import reserve_device_workspace
+
+        reserve_device_workspace(conversion.fp4_linears, seq, device)   # no step grows the recomputation workspace
         previous_tf32 = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = True  # stated policy of the stand-in's FP32 head: TF32 tensor cores
         parameters = sum(p.numel() for p in model.parameters())

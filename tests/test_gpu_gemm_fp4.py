@@ -666,7 +666,8 @@ def test_workspace_form_checks_its_workspace(b200):
     lib = native.load()
     m, n, k = 192, 320, 256
     need = lib.ue5m3_fallback_workspace_bytes(m, n, k)
-    assert need == (2 * b200.FALLBACK_MAX_ROWS + m + n) * k * 2
+    assert need == (2 * b200.FALLBACK_MAX_ROWS + m + n) * k * 2 == b200.fallback_workspace_bytes(m, n, k)
+    assert b200.reserve_fallback_workspace(torch.device("cuda", torch.cuda.current_device()), need) >= need
     assert lib.ue5m3_fallback_workspace_bytes(0, n, k) == 0
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator().manual_seed(3)

@@ -209,6 +209,27 @@ def test_conversion_keeps_parameters_and_rejects_ambiguity():
         convert_linear_modules(torch.nn.Linear(2, 2), selector=select_all_linears)
 
 
+def test_product_plan_of_converted_linears():
+    """plan_fp4_products: the three GEMM shapes of every converted linear for a token count,
+    whether their operands qualify for the packed one-launch quantizers, and the recomputation
+    workspace they ask for (host arithmetic only)."""
+
+    from ue5m3_fp4.nn import ConversionRecord, plan_fp4_products
+
+    records = (ConversionRecord("layers.1.mixer.up_proj", 4096, 21504, False),
+               ConversionRecord("layers.2.mixer.odd", 100, 64, True))
+    plans = plan_fp4_products(records, tokens=8192)
+    assert [(p.product, p.m, p.n, p.k) for p in plans[:3]] == [
+        ("forward", 8192, 21504, 4096), ("data_gradient", 8192, 4096, 21504), ("weight_gradient", 21504, 4096, 8192)]
+    assert all(p.packed_operands for p in plans[:3])
+    assert [p.weight_in_one_launch for p in plans[:3]] == [True, True, False]
+    assert plans[2].workspace_bytes == (2 * 4096 + 21504 + 4096) * 8192 * 2
+    assert [p.packed_operands for p in plans[3:]] == [False, True, True]   # K = 100 is not a multiple of 64
+    assert not any(p.weight_in_one_launch for p in plans[3:])
+    with pytest.raises(ValueError, match="tokens"):
+        plan_fp4_products(records, tokens=0)
+
+
 def test_linear_fails_closed_on_cpu_and_reports_contract_strings():
     layer = UE5M3Linear(64, 32, bias=False, backend="probe_matched", dtype=torch.bfloat16)
     layer.scale_state.begin_step(1)

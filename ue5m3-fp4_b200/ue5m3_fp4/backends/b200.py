@@ -838,6 +838,23 @@ def _fallback_workspace(device: torch.device, size: int) -> Tensor:
     return held
 
 
+def fallback_workspace_bytes(m: int, n: int, k: int) -> int:
+    """Bytes of workspace that the recomputation pass wants for an [m, k] x [n, k] product:
+    (2 x 4096 + m + n) rows of k bf16 values (host arithmetic of ue5m3_fallback_workspace_bytes)."""
+
+    if m <= 0 or n <= 0 or k <= 0:
+        return 0
+    return (2 * FALLBACK_MAX_ROWS + m + n) * k * 2
+
+
+def reserve_fallback_workspace(device: torch.device, size: int) -> int:
+    """Make the recomputation pass's workspace of ``device``'s current stream at least ``size``
+    bytes now; returns the bytes held."""
+
+    with torch.cuda.device(device):
+        return _fallback_workspace(torch.device(device), int(size)).numel()
+
+
 def gemm_fp4_operands(a: Fp4Operand, b: Fp4Operand, *, snap: bool, alpha: "Tensor | EpilogueAlpha | None" = None,
                       bias: Tensor | None = None, out_dtype: torch.dtype = torch.float32,
                       kernel_events: "tuple[torch.cuda.Event, torch.cuda.Event] | None" = None) -> Tensor:

@@ -107,10 +107,62 @@ def convert_linear_modules(
     return tuple(records)
 
 
+@dataclass(frozen=True)
+class ProductPlan:
+    """One of the three GEMMs of a converted linear on the FP4 tensor-core path."""
+
+    module_name: str
+    product: str                 # "forward", "data_gradient" or "weight_gradient"
+    m: int
+    n: int
+    k: int
+    packed_operands: bool        # K % 64 == 0: both operands leave the one-launch operand quantizers
+    weight_in_one_launch: bool   # forward / data gradient: W and W^T come from one read of the weight
+    workspace_bytes: int         # what the recomputation pass wants for this product
+
+
+def plan_fp4_products(records, tokens: int) -> tuple[ProductPlan, ...]:
+    """What a step of ``tokens`` tokens asks of the device for every converted linear: the three
+    products Y = X W^T [tokens, out, in], dX = dY W [tokens, in, out] and dW = dY^T X
+    [out, in, tokens] with the operand constraints of the packed path (reduction axis a
+    multiple of 64) and the recomputation pass's workspace.  Has no counterpart in the
+    reference, whose Triton path has neither packed operands nor a workspace."""
+
+    from ue5m3_fp4.backends import b200
+
+    if tokens <= 0:
+        raise ValueError("tokens must be positive")
+    plans = []
+    for record in records:
+        both = record.in_features % 64 == 0 and record.out_features % 64 == 0
+        for product, (m, n, k) in (
+            ("forward", (tokens, record.out_features, record.in_features)),
+            ("data_gradient", (tokens, record.in_features, record.out_features)),
+            ("weight_gradient", (record.out_features, record.in_features, tokens)),
+        ):
+            plans.append(ProductPlan(record.module_name, product, m, n, k, k % 64 == 0,
+                                     both and product != "weight_gradient", b200.fallback_workspace_bytes(m, n, k)))
+    return tuple(plans)
+
+
+def reserve_device_workspace(records, tokens: int, device: torch.device) -> int:
+    """Size the recomputation pass's per-stream workspace for the largest product of the
+    converted linears now, on ``device``'s current stream, so that no training step grows it.
+    Returns the number of bytes held."""
+
+    from ue5m3_fp4.backends import b200
+
+    need = max((plan.workspace_bytes for plan in plan_fp4_products(records, tokens)), default=0)
+    return b200.reserve_fallback_workspace(device, need)
+
+
 __all__ = [
     "ConversionRecord",
     "LinearSelector",
+    "ProductPlan",
     "convert_linear_modules",
     "exclude_lm_head",
+    "plan_fp4_products",
+    "reserve_device_workspace",
     "select_all_linears",
 ]
