@@ -372,17 +372,22 @@ quantize_operand_t_kernel(const OperandTArgs a) {
     const int64_t krow = r0 + row_base;          // first reduction index of this warp
     const bool rows_valid = krow < a.rows;       // rows % 64 == 0: a 32-row quarter is in or out
 
+    // 16 x 1 blocks need nothing from outside their own 16 rows: their amax is taken in the main
+    // loop below, from the values that are loaded there anyway
+    constexpr bool kAmaxInLoop = B == 16 && !TWO_D && !AMAX_ONLY;
     float m[2][2];
+    if (!kAmaxInLoop) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float u0[16], u1[16];
-        tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u0, u1);
-        if (RHT) { rht16(u0); rht16(u1); }
-        m[h][0] = m[h][1] = 0.0f;
+        for (int h = 0; h < 2; ++h) {
+            float u0[16], u1[16];
+            tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u0, u1);
+            if (RHT) { rht16(u0); rht16(u1); }
+            m[h][0] = m[h][1] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            m[h][0] = fmaxf(m[h][0], fabsf(u0[i]));
-            m[h][1] = fmaxf(m[h][1], fabsf(u1[i]));
+            for (int i = 0; i < 16; ++i) {
+                m[h][0] = fmaxf(m[h][0], fabsf(u0[i]));
+                m[h][1] = fmaxf(m[h][1], fabsf(u1[i]));
+            }
         }
     }
     if (AMAX_ONLY) {
@@ -415,6 +420,14 @@ quantize_operand_t_kernel(const OperandTArgs a) {
         float u[2][16];
         tile_pair_values(tile, kPitch, row_base + 16 * h, word, T(), u[0], u[1]);
         if (RHT) { rht16(u[0]); rht16(u[1]); }
+        if (kAmaxInLoop) {
+            m[h][0] = m[h][1] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                m[h][0] = fmaxf(m[h][0], fabsf(u[0][i]));
+                m[h][1] = fmaxf(m[h][1], fabsf(u[1][i]));
+            }
+        }
         uint32_t rw[2][4];   // random bytes of the 16 rows, per column
         uint32_t sign_even[2][2], sign_odd[2][2];  // [column][half]: sign bytes of rows 0,2,4,6 / 1,3,5,7
         constexpr bool kRawSigns = kSr && sizeof(T) == 2 && !RHT;
